@@ -1,0 +1,183 @@
+/*
+ * kpx.h -- C ABI of the B200 (sm_100a) KV-cache path for the kuiper operator API.
+ *
+ * Every entry point takes plain device/host pointers, integer sizes and a CUDA
+ * stream passed as void* (cudaStream_t); none allocates unless it says so, none
+ * synchronises the stream unless it says so, none aborts: the return value is a
+ * status code (0 = KPX_OK).  There is no CPU fallback: on a machine without a
+ * CUDA device the compute entry points return KPX_ERR_CUDA.
+ *
+ * Each declaration cites the interface of the reference project (paths relative
+ * to its root) that it stands in for.
+ */
+#ifndef KPX_H_
+#define KPX_H_
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KPX_API __attribute__((visibility("default")))
+
+/* Status codes.  0,1,5,7 keep the numeric values of base::StatusCode
+ * (kuiper/include/base/base.h:96-104) so the C++ adapters can forward them. */
+enum {
+  KPX_OK = 0,
+  KPX_ERR_UNIMPLEMENTED = 1,
+  KPX_ERR_INTERNAL = 5,
+  KPX_ERR_INVALID_ARGUMENT = 7,
+  KPX_ERR_OUT_OF_BLOCKS = 8,
+  KPX_ERR_CUDA = 9,
+  KPX_ERR_WORKSPACE_TOO_SMALL = 10,
+  KPX_ERR_DEVICE_TIMEOUT = 11,
+  KPX_ERR_REFCOUNT = 12,
+  KPX_ERR_NOT_FOUND = 13
+};
+
+/* Element types of pools, queries and outputs (base::DataType has Fp32 and Fp16,
+ * kuiper/include/base/base.h:58-64; bf16 is an addition). */
+enum { KPX_F16 = 0, KPX_BF16 = 1, KPX_F32 = 2 };
+
+/* Addressing of a K or V cache for one layer.  Element (block, head, token, i)
+ * lives at  base + block*block_stride + head*head_stride + token*token_stride + i
+ * (strides in elements, int64 throughout).
+ *   paged pool  [num_blocks][kv_heads][block_size][head_size]:
+ *       block_stride = kv_heads*block_size*head_size, head_stride = block_size*head_size,
+ *       token_stride = head_size          -> one (block, head) tile is contiguous
+ *   reference cache [seq_len][kv_heads*head_size] (kuiper/source/model/model.cpp:348-385),
+ *   seen as blocks of block_size consecutive rows with an identity block table:
+ *       block_stride = block_size*kv_dim, head_stride = head_size, token_stride = kv_dim */
+typedef struct kpx_kv_layout {
+  int32_t dtype;        /* KPX_F16 | KPX_BF16 | KPX_F32 */
+  int32_t num_kv_heads;
+  int32_t head_size;    /* 128 */
+  int32_t block_size;   /* 16 tokens */
+  int64_t block_stride;
+  int64_t head_stride;
+  int64_t token_stride;
+  int64_t num_blocks;   /* blocks addressable from base; 0 = unknown (ids are not range-checked) */
+} kpx_kv_layout;
+
+KPX_API const char* kpx_status_string(int status);
+KPX_API int kpx_abi_version(void);
+KPX_API int kpx_device_count(void);
+
+/* Fill *out with the paged-pool layout / with the reference's contiguous layout. */
+KPX_API int kpx_layout_paged(kpx_kv_layout* out, int32_t dtype, int32_t num_kv_heads,
+                             int32_t head_size, int32_t block_size);
+KPX_API int kpx_layout_contiguous(kpx_kv_layout* out, int32_t dtype, int32_t num_kv_heads,
+                                  int32_t head_size, int32_t block_size);
+
+/* ---------------------------------------------------------------- append ----
+ * Scatter num_tokens rows of K and V ([num_tokens, kv_heads*head_size], already
+ * RoPE'd) into the cache: token t goes to slot slot_mapping[t] (= block*block_size
+ * + offset; negative = skip).  If slot_mapping is NULL the rows go to consecutive
+ * slots starting at *pos_dev (a device int32, the reference's GPU-resident
+ * position) plus pos_bias.  Bit-exact copy, 128-bit vectorised.
+ * Replaces copy_to_kv_cache_kernel / _fp16 (kuiper/source/op/kernels/cuda/
+ * kv_cache_kernel.cuh:24-33), fused_kv_cache_update_cu (cuda/fused_kernels.cuh:53-64)
+ * and the prefill cudaMemcpyAsync pair (kuiper/source/model/qwen3.cpp:1224-1241).
+ * v_pool/v_src may be NULL to append K only (KVCacheLayer appends one at a time). */
+KPX_API int kpx_append(void* k_pool, void* v_pool, const kpx_kv_layout* layout, const void* k_src,
+                       const void* v_src, const int64_t* slot_mapping, const int32_t* pos_dev,
+                       int32_t pos_bias, int32_t num_tokens, void* stream);
+
+/* RoPE (half-split pairs (j, j+head_size/2), fp32 math, one rounding at the store)
+ * on num_tokens rows of Q [num_tokens, q_heads*head_size] and K, in place, with
+ * sin/cos read from fp32 tables [max_pos, head_size] at index pos*head_size + 2j;
+ * then, if k_pool is not NULL, the rotated K rows and the V rows are appended as
+ * kpx_append does.  positions is a device int32 array [num_tokens].  The products
+ * are not contracted into FMAs, so the result is bit-identical to the reference
+ * CPU statement when both read the same tables.
+ * Replaces rope_kernel_cu / _gpu_pos / _fp16_gpu_pos / batched_rope_kernel_cu
+ * (kuiper/source/op/kernels/cuda/rope_kernel.cuh:5-28), CPU statement
+ * kuiper/source/op/kernels/cpu/rope_kernel.cpp:58-82.  q or k may be NULL. */
+KPX_API int kpx_rope_append(void* q, void* k, const void* v, int32_t q_heads,
+                            const int32_t* positions, const float* sin_cache,
+                            const float* cos_cache, void* k_pool, void* v_pool,
+                            const kpx_kv_layout* layout, const int64_t* slot_mapping,
+                            int32_t num_tokens, void* stream);
+
+/* fp32 sin/cos tables [max_seq_len, head_size]: table[pos*head_size + k] =
+ * sin/cos(pos * theta^(-k/head_size)).  Replaces sin_cos_cache_calc_cu
+ * (kuiper/source/op/kernels/cuda/rope_kernel.cuh:22-23). */
+KPX_API int kpx_sin_cos_cache(float* sin_cache, float* cos_cache, int32_t head_size,
+                              int32_t max_seq_len, float theta, void* stream);
+
+/* ---------------------------------------------------------------- decode ----
+ * Bytes of device scratch kpx_paged_decode needs on the current device for up
+ * to `batch` sequences (split-KV partials of the persistent CTAs + a status
+ * word).  Does not depend on sequence lengths. */
+KPX_API int64_t kpx_decode_workspace_bytes(int32_t batch, int32_t num_q_heads,
+                                           int32_t num_kv_heads, int32_t head_size);
+
+/* Single-query attention for `batch` sequences: out[b,h,:] = softmax(scale *
+ * q[b,h,:] . K[b, 0..len_b-1, h/kv_mul, :]) V[...], K/V gathered through
+ * block_table[b][0..] (int32 [batch, max_blocks_per_seq] on the device; NULL =
+ * identity table 0,1,2,... which is the reference's contiguous cache).
+ * len_b = seq_lens[b] + len_bias with seq_lens a device int32 array (the
+ * reference's device-resident pos: pass len_bias = 1); if seq_lens is NULL every
+ * sequence has len_bias tokens.  q/out are [batch, num_q_heads*head_size] of the
+ * layout's dtype.  len_b = 0 gives zeros.  All variable state is read from device
+ * memory and the shared-memory size is fixed, so the launch can be captured.
+ * Replaces mha_kernel_cu / _gpu_pos (kuiper/source/op/kernels/cuda/mha_kernel.cuh:4-18),
+ * flash_attention_decode[_fp16][_gpu_pos]_cu and flash_attention2_decode* (cuda/
+ * flash_attention_kernel.cuh:47-61,92-126,181-234); arithmetic statement: cpu/
+ * mha_kernel.cpp:5-61. */
+KPX_API int kpx_paged_decode(void* out, const void* q, const void* k_pool, const void* v_pool,
+                             const kpx_kv_layout* layout, const int32_t* block_table,
+                             int32_t max_blocks_per_seq, const int32_t* seq_lens,
+                             int32_t len_bias, int32_t batch, int32_t num_q_heads, float scale,
+                             void* workspace, int64_t workspace_bytes, void* stream);
+
+/* A workspace starts with a 256-byte header whose first word is a sticky status
+ * the kernels raise (never clear).  kpx_workspace_init zeroes the header (async on
+ * `stream`); call it once after allocating a workspace.  kpx_workspace_status
+ * synchronises the stream, returns the word -- KPX_OK, KPX_ERR_DEVICE_TIMEOUT if a
+ * bounded device-side wait gave up, KPX_ERR_INVALID_ARGUMENT if a block id outside
+ * [0, layout.num_blocks) was met -- and clears it.  No reference counterpart (the
+ * reference does not check its launches on the hot path). */
+KPX_API int kpx_workspace_init(void* workspace, int64_t workspace_bytes, void* stream);
+KPX_API int kpx_workspace_status(void* workspace, void* stream);
+
+/* --------------------------------------------------------------- prefill ----
+ * Causal attention of a chunk of queries against the cache the chunk has
+ * already been appended to.  Sequence b owns query rows
+ * [cu_q_lens[b], cu_q_lens[b+1]) of q/out ([total_q, num_q_heads*head_size]);
+ * its query i sits at position start_pos[b] + i and attends cache positions
+ * 0 .. start_pos[b]+i.  cu_q_lens (int32 [batch+1]) and start_pos (int32 [batch])
+ * are HOST arrays (they size the grid).
+ * Replaces batched_mha_kernel_cu (kuiper/source/op/kernels/cuda/mha_kernel.cuh:20-26),
+ * flash_attention_prefill[_fp16]_cu, flash_attention2_prefill[_fp16]_cu (cuda/
+ * flash_attention_kernel.cuh:27-42,71-86,139-174). */
+KPX_API int64_t kpx_prefill_workspace_bytes(int32_t total_q, int32_t num_q_heads,
+                                            int32_t num_kv_heads, int32_t head_size);
+KPX_API int kpx_paged_prefill(void* out, const void* q, const void* k_pool, const void* v_pool,
+                              const kpx_kv_layout* layout, const int32_t* block_table,
+                              int32_t max_blocks_per_seq, const int32_t* cu_q_lens_host,
+                              const int32_t* start_pos_host, int32_t batch, int32_t num_q_heads,
+                              float scale, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------- block sharing on device --
+ * Copy-on-write: for i < n copy block src_ids[i] to block dst_ids[i] in the K and
+ * the V pool of every layer (pools of consecutive layers are layer_stride
+ * elements apart).  src_ids/dst_ids are device int32 arrays.  No reference
+ * counterpart (the reference cache is never shared between sequences). */
+KPX_API int kpx_cow_copy_blocks(void* k_pool, void* v_pool, const kpx_kv_layout* layout,
+                                int32_t num_layers, int64_t layer_stride, const int32_t* src_ids,
+                                const int32_t* dst_ids, int32_t n, void* stream);
+
+/* refcounts[block_ids[i]] += deltas[i] for i < n (device arrays; duplicates
+ * allowed).  A count that would go below zero, or a block id outside
+ * [0, num_blocks), is left untouched and recorded: *error_count_dev (device
+ * int32, may be NULL) is incremented.  No reference counterpart (the reference
+ * counts references per radix node on the host, radix_tree.h:158-178). */
+KPX_API int kpx_refcount_update(int32_t* refcounts, int32_t num_blocks, const int32_t* block_ids,
+                                const int32_t* deltas, int32_t n, int32_t* error_count_dev,
+                                void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KPX_H_ */

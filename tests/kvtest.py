@@ -1,0 +1,287 @@
+"""Shared test helpers: the CPU oracle binding, seeded inputs, paged scenarios, tolerances.
+
+Only test code (and bench.py's cpu_baseline / reference arm) may touch the oracle.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from dataclasses import dataclass
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent.parent
+ORACLE_DIR = ROOT / "oracle"
+
+# north-star tolerance for attention outputs against the fp32 oracle
+ATOL = 2e-3
+RTOL = 1e-2
+REL_FLOOR = 1e-2  # relative error is measured against max(|a|, |b|, REL_FLOOR)
+
+
+# ----------------------------------------------------------------------------- oracle
+class Oracle:
+    def __init__(self, lib: C.CDLL):
+        self.lib = lib
+        f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+        f64p = np.ctypeslib.ndpointer(np.float64, flags="C_CONTIGUOUS")
+        i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
+        i64p = np.ctypeslib.ndpointer(np.int64, flags="C_CONTIGUOUS")
+        u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
+        i32 = C.c_int32
+        sig = {
+            "orc_sin_cos_cache": [i32, i32, C.c_float, f32p, f32p],
+            "orc_rope": [i32, i32, i32, C.c_void_p, C.c_void_p, i32, f32p, f32p],
+            "orc_rope_batched": [i32, i32, i32, i32, i32, C.c_void_p, C.c_void_p, f32p, f32p],
+            "orc_softmax_inplace": [f32p, i32],
+            "orc_mha": [i32, i32, i32, i32, i32, i32, i32, f32p, f32p, f32p, f32p, f32p],
+            "orc_mha_f64": [i32, i32, i32, i32, i32, i32, i32, f64p, f32p, f32p, f32p],
+            "orc_mha_prefill": [i32, i32, i32, i32, i32, i32, i32, i32, f32p, f32p, f32p, f32p, i32],
+            "orc_append_contiguous": [f32p, f32p, i32, i32, i32, i32],
+            "orc_append_paged": [u8p, u8p, i64p, i32, i32, i32, i32, i32],
+            "orc_gather_paged": [u8p, u8p, i32p, i32, i32, i32, i32, i32],
+            "orc_paged_decode": [f32p, f32p, f32p, f32p, i32p, i32, i32p, i32, i32, i32, i32, i32, i32],
+            "orc_max_threads": [],
+        }
+        for name, args in sig.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = i32 if name == "orc_max_threads" else None
+
+    # thin numpy wrappers -------------------------------------------------------------
+    def sin_cos_cache(self, head_size, max_seq_len, theta=1e6):
+        s = np.empty((max_seq_len, head_size), np.float32)
+        c = np.empty((max_seq_len, head_size), np.float32)
+        self.lib.orc_sin_cos_cache(head_size, max_seq_len, theta, s, c)
+        return s, c
+
+    def rope_batched(self, start_pos, q, k, head_size, sin, cos):
+        """q [n, dim] / k [n, kv_dim] float32, rotated in place (either may be None)."""
+        n = (q if q is not None else k).shape[0]
+        dim = q.shape[1] if q is not None else k.shape[1]
+        kv_dim = k.shape[1] if k is not None else 0
+        self.lib.orc_rope_batched(start_pos, n, dim, kv_dim, head_size,
+                                  q.ctypes.data if q is not None else None,
+                                  k.ctypes.data if k is not None else None, sin, cos)
+
+    def rope(self, pos, q, k, head_size, sin, cos):
+        dim = q.shape[0] if q is not None else k.shape[0]
+        kv_dim = k.shape[0] if k is not None else 0
+        self.lib.orc_rope(dim, kv_dim, head_size, q.ctypes.data if q is not None else None,
+                          k.ctypes.data if k is not None else None, pos, sin, cos)
+
+    def mha(self, pos, head_num, layer_index, seq_len, kv_dim, kv_mul, head_size, q, kc, vc):
+        out = np.empty(head_num * head_size, np.float32)
+        score = np.empty(head_num * seq_len, np.float32)
+        self.lib.orc_mha(pos, head_num, layer_index, seq_len, kv_dim, kv_mul, head_size, out,
+                         np.ascontiguousarray(q, np.float32), score, kc, vc)
+        return out
+
+    def mha_f64(self, pos, head_num, layer_index, seq_len, kv_dim, kv_mul, head_size, q, kc, vc):
+        out = np.empty(head_num * head_size, np.float64)
+        self.lib.orc_mha_f64(pos, head_num, layer_index, seq_len, kv_dim, kv_mul, head_size, out,
+                             np.ascontiguousarray(q, np.float32), kc, vc)
+        return out
+
+    def mha_prefill(self, start_pos, q, head_num, seq_len, kv_dim, kv_mul, head_size, kc, vc,
+                    threads=1):
+        n = q.shape[0]
+        out = np.empty((n, head_num * head_size), np.float32)
+        self.lib.orc_mha_prefill(start_pos, n, head_num, 0, seq_len, kv_dim, kv_mul, head_size, out,
+                                 np.ascontiguousarray(q, np.float32), kc, vc, threads)
+        return out
+
+    def append_paged(self, pool, src, slot_mapping, kv_heads, head_size, block_size):
+        """pool [nblk, kv_heads, block_size, head_size], src [n, kv_heads*head_size]; raw bytes."""
+        elt = pool.dtype.itemsize
+        self.lib.orc_append_paged(pool.view(np.uint8).reshape(-1), np.ascontiguousarray(src).view(np.uint8).reshape(-1),
+                                  np.ascontiguousarray(slot_mapping, np.int64), src.shape[0],
+                                  kv_heads, head_size, block_size, elt)
+
+    def gather_paged(self, pool, table_row, length, kv_heads, head_size, block_size):
+        dst = np.empty((length, kv_heads * head_size), pool.dtype)
+        self.lib.orc_gather_paged(dst.view(np.uint8).reshape(-1), pool.view(np.uint8).reshape(-1),
+                                  np.ascontiguousarray(table_row, np.int32), length, kv_heads,
+                                  head_size, block_size, pool.dtype.itemsize)
+        return dst
+
+    def paged_decode(self, q, k_pool, v_pool, block_table, seq_lens, head_num, kv_heads, head_size,
+                     block_size, threads=1):
+        """All fp32.  q [B, head_num*head_size]; pools [nblk, kv_heads, bs, hs]."""
+        b = q.shape[0]
+        out = np.empty((b, head_num * head_size), np.float32)
+        bt = np.ascontiguousarray(block_table, np.int32)
+        self.lib.orc_paged_decode(out, np.ascontiguousarray(q, np.float32),
+                                  np.ascontiguousarray(k_pool, np.float32).reshape(-1),
+                                  np.ascontiguousarray(v_pool, np.float32).reshape(-1), bt,
+                                  bt.shape[1], np.ascontiguousarray(seq_lens, np.int32), b, head_num,
+                                  kv_heads, head_size, block_size, threads)
+        return out
+
+    def max_threads(self):
+        return int(self.lib.orc_max_threads())
+
+
+def load_oracle() -> Oracle:
+    so = ORACLE_DIR / "liborinkv_oracle.so"
+    src = ORACLE_DIR / "kv_oracle.c"
+    if not so.exists() or so.stat().st_mtime < src.stat().st_mtime:
+        subprocess.run(["make", "-C", str(ORACLE_DIR), "all"], check=True, capture_output=True)
+    return Oracle(C.CDLL(str(so)))
+
+
+# --------------------------------------------------------------------- dtype helpers
+def bf16_round(x: np.ndarray) -> np.ndarray:
+    """float32 -> bf16 (round to nearest even) kept as uint16 bit patterns."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    rounded = u + 0x7FFF + ((u >> 16) & 1)
+    return (rounded >> 16).astype(np.uint16)
+
+
+def bf16_to_f32(u16: np.ndarray) -> np.ndarray:
+    return (u16.astype(np.uint32) << 16).view(np.float32)
+
+
+def to_storage(x32: np.ndarray, dtype: str) -> np.ndarray:
+    """Quantise fp32 data to the storage type; returns the array as stored
+    (float16 / uint16-bf16-bits / float32)."""
+    if dtype == "f16":
+        return x32.astype(np.float16)
+    if dtype == "bf16":
+        return bf16_round(x32)
+    return np.ascontiguousarray(x32, np.float32)
+
+
+def storage_to_f32(x: np.ndarray, dtype: str) -> np.ndarray:
+    if dtype == "f16":
+        return x.astype(np.float32)
+    if dtype == "bf16":
+        return bf16_to_f32(x)
+    return np.ascontiguousarray(x, np.float32)
+
+
+def torch_dtype(dtype: str):
+    import torch
+    return {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[dtype]
+
+
+def to_device(x: np.ndarray, dtype: str):
+    """numpy storage array -> CUDA tensor of the matching torch dtype (bit-exact)."""
+    import torch
+    t = torch.from_numpy(np.ascontiguousarray(x))
+    if dtype == "bf16":
+        t = t.view(torch.bfloat16)
+    return t.cuda()
+
+
+def from_device(t, dtype: str) -> np.ndarray:
+    import torch
+    t = t.detach().cpu().contiguous()
+    if dtype == "bf16":
+        return t.view(torch.uint16).numpy() if hasattr(torch, "uint16") else t.view(torch.int16).numpy().view(np.uint16)
+    return t.numpy()
+
+
+def poison(shape, dtype: str) -> np.ndarray:
+    """A pool full of NaNs: any read outside the block table shows up in the output."""
+    if dtype == "f16":
+        return np.full(shape, np.nan, np.float16)
+    if dtype == "bf16":
+        return np.full(shape, 0x7FC0, np.uint16)
+    return np.full(shape, np.nan, np.float32)
+
+
+# ------------------------------------------------------------------------ tolerances
+def attention_errors(got: np.ndarray, ref: np.ndarray):
+    got = np.asarray(got, np.float64)
+    ref = np.asarray(ref, np.float64)
+    diff = np.abs(got - ref)
+    denom = np.maximum(np.maximum(np.abs(got), np.abs(ref)), REL_FLOOR)
+    return float(diff.max(initial=0.0)), float((diff / denom).max(initial=0.0))
+
+
+def assert_attention_close(got, ref, what=""):
+    """max-abs <= 2e-3 and max-rel <= 1e-2 (relative to max(|a|,|b|,1e-2))."""
+    assert np.all(np.isfinite(np.asarray(got, np.float64))), f"{what}: non-finite output"
+    max_abs, max_rel = attention_errors(got, ref)
+    assert max_abs <= ATOL, f"{what}: max abs err {max_abs:.3e} > {ATOL}"
+    assert max_rel <= RTOL, f"{what}: max rel err {max_rel:.3e} > {RTOL}"
+    return max_abs, max_rel
+
+
+# ------------------------------------------------------------------- paged scenarios
+@dataclass
+class PagedCase:
+    """A batch of sequences laid out in a block pool through a seeded random block table."""
+    dtype: str
+    q_heads: int
+    kv_heads: int
+    head_size: int
+    block_size: int
+    seq_lens: np.ndarray          # int32 [B]
+    num_blocks: int
+    block_table: np.ndarray       # int32 [B, max_blocks], -1 = unmapped
+    k_rows: np.ndarray            # storage dtype [total_tokens, kv_dim]  (already RoPE'd)
+    v_rows: np.ndarray
+    slot_mapping: np.ndarray      # int64 [total_tokens]
+    q: np.ndarray                 # storage dtype [B, q_heads*head_size]
+
+    @property
+    def kv_dim(self):
+        return self.kv_heads * self.head_size
+
+    @property
+    def total_tokens(self):
+        return int(self.seq_lens.sum())
+
+
+def make_paged_case(seed, dtype, q_heads, kv_heads, seq_lens, head_size=128, block_size=16,
+                    pool_factor=1.25, extra_blocks=3, scale_k=1.0) -> PagedCase:
+    """Q/K/V ~ N(0,1) from `seed`; block table = seeded random permutation of the pool."""
+    rng = np.random.default_rng(seed)
+    seq_lens = np.asarray(seq_lens, np.int32)
+    b = len(seq_lens)
+    nblk = [(int(l) + block_size - 1) // block_size for l in seq_lens]
+    need = sum(nblk)
+    num_blocks = int(np.ceil(need * pool_factor)) + extra_blocks
+    perm = rng.permutation(num_blocks).astype(np.int32)
+    max_blocks = max(max(nblk, default=0), 1)
+    table = np.full((b, max_blocks), -1, np.int32)
+    slots = []
+    c = 0
+    for i, n in enumerate(nblk):
+        table[i, :n] = perm[c:c + n]
+        c += n
+        pos = np.arange(int(seq_lens[i]), dtype=np.int64)
+        slots.append(table[i, pos // block_size].astype(np.int64) * block_size + pos % block_size)
+    total = int(seq_lens.sum())
+    kv_dim = kv_heads * head_size
+    k32 = (rng.standard_normal((total, kv_dim), np.float32) * scale_k).astype(np.float32)
+    v32 = rng.standard_normal((total, kv_dim), np.float32)
+    q32 = rng.standard_normal((b, q_heads * head_size), np.float32)
+    return PagedCase(dtype, q_heads, kv_heads, head_size, block_size, seq_lens, num_blocks, table,
+                     to_storage(k32, dtype), to_storage(v32, dtype),
+                     np.concatenate(slots) if slots else np.zeros(0, np.int64),
+                     to_storage(q32, dtype))
+
+
+def oracle_pools(oracle: Oracle, case: PagedCase):
+    """Build the K and V pools on the CPU (poisoned outside the appended slots)."""
+    shape = (case.num_blocks, case.kv_heads, case.block_size, case.head_size)
+    kp, vp = poison(shape, case.dtype), poison(shape, case.dtype)
+    if case.total_tokens:
+        oracle.append_paged(kp, case.k_rows, case.slot_mapping, case.kv_heads, case.head_size,
+                            case.block_size)
+        oracle.append_paged(vp, case.v_rows, case.slot_mapping, case.kv_heads, case.head_size,
+                            case.block_size)
+    return kp, vp
+
+
+def oracle_decode(oracle: Oracle, case: PagedCase, kp, vp, threads=1):
+    k32 = storage_to_f32(kp, case.dtype)  # poison stays: the oracle must never read it
+    v32 = storage_to_f32(vp, case.dtype)
+    table = np.where(case.block_table < 0, 0, case.block_table)
+    return oracle.paged_decode(storage_to_f32(case.q, case.dtype), k32, v32, table, case.seq_lens,
+                               case.q_heads, case.kv_heads, case.head_size, case.block_size,
+                               threads)
