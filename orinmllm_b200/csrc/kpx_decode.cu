@@ -10,14 +10,16 @@
 // (running max, sum, un-normalised accumulator) per CTA in the workspace and a
 // small second kernel merges them.
 //
-// Inside a CTA a producer warp gathers K/V tiles through the block table with
-// cp.async.bulk (the TMA engine) into a ring of shared-memory stages guarded by
-// full/empty mbarriers; 4 consumer warps per group of up to 4 query heads each
-// take one block of the stage, so a K/V byte is fetched from HBM once for all
-// query heads that share the KV head.  The math is fp32 on CUDA cores (packed
-// fp32x2 FMAs), softmax is online with warp shuffles.  Every mbarrier wait is
-// bounded; a wait that gives up raises the workspace status word and the CTA
-// drains without touching shared data again.
+// Inside a CTA, K/V tiles are gathered through the block table with cp.async.bulk
+// (the TMA engine) into a ring of shared-memory stages guarded by full/empty
+// mbarriers; warp 0 issues the copies for the stage kStages ahead right after it
+// has finished its share of the current one (a dedicated producer warp would push
+// one scheduler to 3 warps and cap every thread at 168 registers).  4 warps per
+// group of up to 4 query heads each take one block of the stage, so a K/V byte is
+// fetched from HBM once for all query heads that share the KV head.  The math is
+// fp32 on CUDA cores (packed fp32x2 FMAs), softmax is online with warp shuffles.
+// Every mbarrier wait is bounded; a wait that gives up raises the workspace status
+// word and the CTA drains without touching shared data again.
 #include "kpx_common.cuh"
 
 namespace kpx {
@@ -53,7 +55,7 @@ struct Cfg {
   static constexpr int kStageB = 2 * kBPS * kTileB;             // K then V
   static constexpr int kStages = (kEltB == 2) ? (HG == 1 ? 3 : 5) : (HG == 1 ? 3 : 3);
   static constexpr int kConsumerWarps = kBPS * HG;
-  static constexpr int kThreads = 32 * (kConsumerWarps + 1);
+  static constexpr int kThreads = 32 * kConsumerWarps;
   static constexpr int kCtasPerSm = (kEltB == 2 && HG == 1) ? 2 : 1;
   // shared memory carve-up (bytes)
   static constexpr int kOffBars = kStages * kStageB;
@@ -186,79 +188,70 @@ paged_decode_kernel(const DecodeParams p) {
   if (u0 >= u1) return;
   const int n_units = int(u1 - u0);
 
-  if (warp == C::kConsumerWarps) {
-    // =============================== producer warp ===============================
-    Cursor cur;
-    cur.locate(p, prefix, u0);
-    bool aborted = false;
-    const int my_blk = lane & 3;  // lanes 0..3 fetch the block ids of the stage
-    auto load_id = [&](const Cursor& c) -> int {
-      int blk = c.off * kBPS + my_blk;
-      int nblk = (c.len + kBS - 1) / kBS;
-      if (lane >= kBPS || blk >= nblk) return -1;
-      int id = p.block_table ? p.block_table[int64_t(c.b) * p.max_blocks_per_seq + blk] : blk;
-      if (id < 0 || (p.num_blocks > 0 && id >= p.num_blocks)) {
-        atomicMax(p.status, KPX_ERR_INVALID_ARGUMENT);
-        id = 0;
-      }
-      return id;
-    };
-    int next_id = load_id(cur);
-    for (int it = 0; it < n_units; ++it) {
-      const int slot = it % C::kStages;
-      const Cursor here = cur;
-      const int my_id = next_id;
-      cur.advance(p, prefix);
-      if (it + 1 < n_units) next_id = load_id(cur);  // in flight while we wait below
-      if (it >= C::kStages && !aborted) {
-        if (!mbar_wait_bounded(empty_bar + slot, ((it / C::kStages) - 1) & 1)) aborted = true;
-      }
-      aborted = __any_sync(0xffffffffu, aborted || *reinterpret_cast<volatile int*>(abort_flag));
-      if (aborted) break;
-      const int nblk = (here.len + kBS - 1) / kBS;
-      const int nb = min(kBPS, nblk - here.off * kBPS);
-      uint8_t* stage = smem + slot * C::kStageB;
-      if (p.tile_contig) {
-        if (lane == 0) mbar_arrive_expect_tx(full_bar + slot, uint32_t(nb) * 2u * C::kTileB);
-        __syncwarp();
-        // lane -> (block = lane>>1, K/V = lane&1)
-        int blk = lane >> 1, which = lane & 1;
-        int id = __shfl_sync(0xffffffffu, my_id, blk & 3);
-        if (lane < 2 * nb) {
-          const uint8_t* src = (which ? p.v_pool : p.k_pool) + int64_t(id) * p.block_stride_b +
-                               int64_t(here.kvh) * p.head_stride_b;
-          bulk_g2s(stage + which * (kBPS * C::kTileB) + blk * C::kTileB, src, C::kTileB,
-                   full_bar + slot);
-        }
-      } else {
-        // strided rows (the reference's token-major cache): one bulk copy per valid row
-        constexpr int kRowB = kD * C::kEltB;
-        int rows_total = min(here.len - here.off * kBPS * kBS, kBPS * kBS);
-        if (lane == 0) mbar_arrive_expect_tx(full_bar + slot, uint32_t(rows_total) * 2u * kRowB);
-        __syncwarp();
-        for (int c = lane; c < 2 * kBPS * kBS; c += 32) {
-          int blk = c >> 5, which = (c >> 4) & 1, row = c & 15;
-          int id = __shfl_sync(0xffffffffu, my_id, blk);
-          if (blk * kBS + row < rows_total) {
-            const uint8_t* src = (which ? p.v_pool : p.k_pool) + int64_t(id) * p.block_stride_b +
-                                 int64_t(here.kvh) * p.head_stride_b + int64_t(row) * p.token_stride_b;
-            bulk_g2s(stage + which * (kBPS * C::kTileB) + blk * C::kTileB + row * kRowB, src, kRowB,
-                     full_bar + slot);
-          }
-        }
-      }
+  // ============================ producer role (warp 0) ============================
+  // Warp 0 doubles as the producer: after it has finished a stage it refills that
+  // slot with the unit kStages ahead.  Lanes 0..3 fetch the block ids of a unit one
+  // iteration before they are needed, so the table lookup is off the critical path.
+  Cursor pcur;            // next unit to issue
+  int p_next_id = -1;     // block id (lanes 0..3) of the unit at pcur
+  int p_issued = 0;       // units issued so far
+  auto load_id = [&](const Cursor& c) -> int {
+    int blk = c.off * kBPS + (lane & 3);
+    int nblk = (c.len + kBS - 1) / kBS;
+    if (lane >= kBPS || blk >= nblk) return -1;
+    int id = p.block_table ? p.block_table[int64_t(c.b) * p.max_blocks_per_seq + blk] : blk;
+    if (id < 0 || (p.num_blocks > 0 && id >= p.num_blocks)) {
+      atomicMax(p.status, KPX_ERR_INVALID_ARGUMENT);
+      id = 0;
     }
-    if (aborted) {
-      if (lane == 0) {
-        *reinterpret_cast<volatile int*>(abort_flag) = 1;
-        atomicMax(p.status, KPX_ERR_DEVICE_TIMEOUT);
+    return id;
+  };
+  // issue the copies of the unit at pcur into `slot` (the slot must be free), then
+  // step pcur and prefetch the ids of the following unit
+  auto issue_next = [&]() {
+    const int slot = p_issued % C::kStages;
+    const Cursor here = pcur;
+    const int my_id = p_next_id;
+    const int nblk = (here.len + kBS - 1) / kBS;
+    const int nb = min(kBPS, nblk - here.off * kBPS);
+    uint8_t* stage = smem + slot * C::kStageB;
+    if (p.tile_contig) {
+      if (lane == 0) mbar_arrive_expect_tx(full_bar + slot, uint32_t(nb) * 2u * C::kTileB);
+      __syncwarp();
+      int blk = lane >> 1, which = lane & 1;  // lane -> (block, K/V)
+      int id = __shfl_sync(0xffffffffu, my_id, blk & 3);
+      if (lane < 2 * nb) {
+        const uint8_t* src = (which ? p.v_pool : p.k_pool) + int64_t(id) * p.block_stride_b +
+                             int64_t(here.kvh) * p.head_stride_b;
+        bulk_g2s(stage + which * (kBPS * C::kTileB) + blk * C::kTileB, src, C::kTileB,
+                 full_bar + slot);
       }
     } else {
-      // do not retire while bulk copies may still be landing in this CTA's shared memory
-      for (int it = max(0, n_units - C::kStages); it < n_units; ++it)
-        mbar_wait_bounded(full_bar + (it % C::kStages), (it / C::kStages) & 1);
+      // strided rows (the reference's token-major cache): one bulk copy per valid row
+      constexpr int kRowB = kD * C::kEltB;
+      int rows_total = min(here.len - here.off * kBPS * kBS, kBPS * kBS);
+      if (lane == 0) mbar_arrive_expect_tx(full_bar + slot, uint32_t(rows_total) * 2u * kRowB);
+      __syncwarp();
+      for (int c = lane; c < 2 * kBPS * kBS; c += 32) {
+        int blk = c >> 5, which = (c >> 4) & 1, row = c & 15;
+        int id = __shfl_sync(0xffffffffu, my_id, blk);
+        if (blk * kBS + row < rows_total) {
+          const uint8_t* src = (which ? p.v_pool : p.k_pool) + int64_t(id) * p.block_stride_b +
+                               int64_t(here.kvh) * p.head_stride_b + int64_t(row) * p.token_stride_b;
+          bulk_g2s(stage + which * (kBPS * C::kTileB) + blk * C::kTileB + row * kRowB, src, kRowB,
+                   full_bar + slot);
+        }
+      }
     }
-    return;
+    ++p_issued;
+    pcur.advance(p, prefix);
+    if (p_issued < n_units) p_next_id = load_id(pcur);
+  };
+  if (warp == 0) {
+    pcur.locate(p, prefix, u0);
+    p_next_id = load_id(pcur);
+    const int pre = min(n_units, C::kStages);
+    for (int i = 0; i < pre; ++i) issue_next();
   }
 
   // ================================ consumer warps =================================
@@ -402,7 +395,7 @@ paged_decode_kernel(const DecodeParams p) {
         atomicMax(p.status, KPX_ERR_DEVICE_TIMEOUT);
       }
     }
-    aborted = __any_sync(0xffffffffu, aborted);
+    aborted = __any_sync(0xffffffffu, aborted || *reinterpret_cast<volatile int*>(abort_flag) != 0);
     const int blk = cur.off * kBPS + wb;
     const int nvalid = cur.len - blk * kBS;  // tokens of this block that exist (may be <= 0)
     if (!aborted && nvalid > 0) {
@@ -515,6 +508,16 @@ paged_decode_kernel(const DecodeParams p) {
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(empty_bar + slot);
+    if (warp == 0 && p_issued < n_units) {
+      // refill this slot once all consumer warps have released it
+      if (!aborted && !mbar_wait_bounded(empty_bar + slot, (it / C::kStages) & 1)) {
+        aborted = true;
+        *reinterpret_cast<volatile int*>(abort_flag) = 1;
+        atomicMax(p.status, KPX_ERR_DEVICE_TIMEOUT);
+      }
+      aborted = __any_sync(0xffffffffu, aborted);
+      if (!aborted) issue_next();
+    }
 
     const Cursor item = cur;
     const bool left = cur.advance(p, prefix);
@@ -585,11 +588,13 @@ __global__ void __launch_bounds__(kD) decode_merge_kernel(const DecodeParams p, 
   for (int h = 0; h < p.kv_mul; ++h) {
     float M = -INFINITY;
     for (int c = c_first; c <= c_last; ++c) {
+      if (range_start(total, c, G) >= range_start(total, c + 1, G)) continue;  // CTA had no units
       int slot = (s_i < range_start(total, c, G)) ? 2 * c : 2 * c + 1;
       M = fmaxf(M, p.partials[int64_t(slot) * slot_floats + hq_total * kD + h]);
     }
     float L = 0.f, O = 0.f;
     for (int c = c_first; c <= c_last; ++c) {
+      if (range_start(total, c, G) >= range_start(total, c + 1, G)) continue;
       int slot = (s_i < range_start(total, c, G)) ? 2 * c : 2 * c + 1;
       const float* ps = p.partials + int64_t(slot) * slot_floats;
       float mw = ps[hq_total * kD + h];

@@ -201,11 +201,18 @@ def attention_errors(got: np.ndarray, ref: np.ndarray):
     return float(diff.max(initial=0.0)), float((diff / denom).max(initial=0.0))
 
 
-def assert_attention_close(got, ref, what=""):
-    """max-abs <= 2e-3 and max-rel <= 1e-2 (relative to max(|a|,|b|,1e-2))."""
+def assert_attention_close(got, ref, what="", out_dtype="f16"):
+    """max-abs <= 2e-3 and max-rel <= 1e-2 (relative to max(|a|,|b|,1e-2)) against the fp32
+    oracle.  A bf16 OUTPUT cannot meet 2e-3 absolute above |x| = 0.5 whatever the kernel does
+    (its rounding step alone is 2^-8 relative), so for bf16 outputs the absolute bound is
+    2e-3 + 2^-8 * |ref|: the north-star bound plus the half-ulp of the mandatory final rounding."""
     assert np.all(np.isfinite(np.asarray(got, np.float64))), f"{what}: non-finite output"
     max_abs, max_rel = attention_errors(got, ref)
-    assert max_abs <= ATOL, f"{what}: max abs err {max_abs:.3e} > {ATOL}"
+    if out_dtype == "bf16":
+        excess = np.abs(np.asarray(got, np.float64) - ref) - (ATOL + np.abs(np.asarray(ref, np.float64)) / 256.0)
+        assert excess.max(initial=-1.0) <= 0.0, f"{what}: abs err beyond 2e-3 + bf16 half-ulp by {excess.max():.3e}"
+    else:
+        assert max_abs <= ATOL, f"{what}: max abs err {max_abs:.3e} > {ATOL}"
     assert max_rel <= RTOL, f"{what}: max rel err {max_rel:.3e} > {RTOL}"
     return max_abs, max_rel
 

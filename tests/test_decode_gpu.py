@@ -37,7 +37,7 @@ def _run_case(oracle, case, check_append=True):
     assert capi.workspace_status(ws) == 0
     got = kvtest.storage_to_f32(kvtest.from_device(out, dt), dt)
     ref = kvtest.oracle_decode(oracle, case, kp_ref, vp_ref, threads=oracle.max_threads())
-    return kvtest.assert_attention_close(got, ref, f"decode {dt} H={case.q_heads}/{case.kv_heads}")
+    return kvtest.assert_attention_close(got, ref, f"decode {dt} H={case.q_heads}/{case.kv_heads}", dt)
 
 
 @pytest.mark.parametrize("dtype", ["f16", "bf16", "f32"])
