@@ -96,7 +96,7 @@ extern "C" int kpx_layout_contiguous(kpx_kv_layout* out, int32_t dtype, int32_t 
 
 extern "C" int kpx_workspace_init(void* workspace, int64_t workspace_bytes, void* stream) {
   if (!workspace || workspace_bytes < 256) return KPX_ERR_INVALID_ARGUMENT;
-  KPX_CUDA_TRY(cudaMemsetAsync(workspace, 0, 256, static_cast<cudaStream_t>(stream)));
+  KPX_CUDA_TRY(cudaMemsetAsync(workspace, 0, size_t(workspace_bytes), static_cast<cudaStream_t>(stream)));
   return KPX_OK;
 }
 

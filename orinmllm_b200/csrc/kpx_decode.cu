@@ -1,34 +1,35 @@
-// Paged GQA decode attention for sm_100a: persistent split-KV kernel + merge.
+// Paged GQA decode attention for sm_100a: warp-granular split-KV streaming + merge.
 //
-// Work decomposition.  The cache of sequence b holds len_b tokens in blocks of 16;
-// a "stage unit" is 4 consecutive blocks (64 tokens) of one (sequence, kv head)
-// item.  All stage units of all items are laid on one line (sequence-major, kv
-// head next) and cut into G equal contiguous ranges, one per persistent CTA
-// (G = resident CTAs on the GPU), so every CTA streams the same number of bytes
-// whatever the spread of sequence lengths.  A CTA that covers an item completely
-// writes its output directly; an item cut by a range boundary leaves one partial
-// (running max, sum, un-normalised accumulator) per CTA in the workspace and a
-// small second kernel merges them.
+// Work decomposition.  The cache of sequence b holds len_b tokens in blocks of 16.
+// An "item" is one (sequence, kv head, query-head group) triple; its work is the
+// sequence's blocks.  All blocks of all items are laid on one line (sequence-major)
+// and cut into W equal contiguous ranges, one per *warp* of a persistent grid (one
+// CTA per SM, 12 warps per CTA for 16-bit caches), so every warp streams the same
+// number of bytes whatever the spread of sequence lengths.  A warp that covers an
+// item completely writes its output directly; an item cut by a range boundary
+// leaves one partial (running max, sum, un-normalised accumulator) per warp in the
+// workspace, and a small second kernel merges the partials.
 //
-// Inside a CTA, K/V tiles are gathered through the block table with cp.async.bulk
-// (the TMA engine) into a ring of shared-memory stages guarded by full/empty
-// mbarriers; warp 0 issues the copies for the stage kStages ahead right after it
-// has finished its share of the current one (a dedicated producer warp would push
-// one scheduler to 3 warps and cap every thread at 168 registers).  4 warps per
-// group of up to 4 query heads each take one block of the stage, so a K/V byte is
-// fetched from HBM once for all query heads that share the KV head.  The math is
-// fp32 on CUDA cores (packed fp32x2 FMAs), softmax is online with warp shuffles.
-// Every mbarrier wait is bounded; a wait that gives up raises the workspace status
-// word and the CTA drains without touching shared data again.
+// Each warp is its own producer and consumer: it owns two K and two V tile slots in
+// shared memory, fetches the (block, kv head) tiles of its range through the block
+// table with cp.async.bulk (the TMA engine, completion on per-slot mbarriers), and
+// refills a slot the moment it has finished reading it -- the K slot right after
+// the score pass, the V slot after the output pass.  There is no cross-warp
+// synchronisation after the prologue.  A warp serves up to 4 query heads of the KV
+// head from one tile read, so a K/V byte crosses HBM once per 4 query heads.  The
+// math is fp32 on CUDA cores (packed fp32x2 FMAs); softmax is online with warp
+// shuffles.  Every mbarrier wait is bounded; a wait that gives up raises the
+// workspace status word and the warp retires.
+#include <type_traits>
+
 #include "kpx_common.cuh"
 
 namespace kpx {
 namespace {
 
-constexpr int kD = 128;       // head size
-constexpr int kBS = 16;       // tokens per block
-constexpr int kBPS = 4;       // blocks per stage (= consumer warps per head group)
-constexpr int kMaxBatch = 1024;  // sequences per launch (prefix table lives in smem)
+constexpr int kD = 128;          // head size
+constexpr int kBS = 16;          // tokens per block
+constexpr int kMaxBatch = 1024;  // sequences per launch (their block prefix lives in smem)
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct DecodeParams {
@@ -39,136 +40,121 @@ struct DecodeParams {
   const int32_t* block_table;
   const int32_t* seq_lens;
   float* partials;
+  int32_t* counters;  // one per item, zero between launches
   int32_t* status;
   int64_t block_stride_b, head_stride_b, token_stride_b;  // bytes
   int64_t num_blocks;
   int32_t max_blocks_per_seq, len_bias, batch;
   int32_t num_q_heads, num_kv_heads, kv_mul;
+  int32_t head_groups;  // ceil(kv_mul / QH)
   int32_t tile_contig;
   float qscale;  // softmax scale * log2(e)
 };
 
-template <typename T, int QH, int HG>
+template <typename T, int QH, int NW, int NS>
 struct Cfg {
   static constexpr int kEltB = sizeof(T);
-  static constexpr int kTileB = kBS * kD * kEltB;               // one (block, head) tile
-  static constexpr int kStageB = 2 * kBPS * kTileB;             // K then V
-  static constexpr int kStages = (kEltB == 2) ? (HG == 1 ? 3 : 5) : (HG == 1 ? 3 : 3);
-  static constexpr int kConsumerWarps = kBPS * HG;
-  static constexpr int kThreads = 32 * kConsumerWarps;
-  static constexpr int kCtasPerSm = (kEltB == 2 && HG == 1) ? 2 : 1;
-  // shared memory carve-up (bytes)
-  static constexpr int kOffBars = kStages * kStageB;
-  static constexpr int kOffPrefix = kOffBars + 2 * kStages * 8 + 16;
+  static constexpr int kTileB = kBS * kD * kEltB;  // one (block, head) tile of K or of V
+  static constexpr int kWarps = NW;  // NS = K slots (and V slots) per warp
+  static constexpr int kThreads = 32 * kWarps;
+  static constexpr int kWarpRingB = 2 * NS * kTileB;  // K slots then V slots
+  static constexpr int kOffBars = kWarps * kWarpRingB;
+  static constexpr int kOffPrefix = kOffBars + kWarps * 2 * NS * 8;
   static constexpr int kOffP = kOffPrefix + (kMaxBatch + 1) * 4 + 12;
-  static constexpr int kOffMerge = kOffP + kConsumerWarps * kBS * 4 * 4;
-  static constexpr int kMergeFloats = kBPS * QH * (kD + 2);  // per head group
-  static constexpr int kSmem = kOffMerge + HG * kMergeFloats * 4;
-  static constexpr int kPartialFloats = HG * QH * (kD + 2);  // one workspace slot
+  static constexpr int kSmem = kOffP + kWarps * 2 * kBS * 4 * 4;  // two weight buffers per warp
+  // one workspace slot: QH accumulators of 128, then QH maxima, QH sums; padded so that
+  // every slot starts on a 16-byte boundary (the assembling warp reads float4)
+  static constexpr int kPartialFloats = QH * kD + 8;
 };
 
 __device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
   int len = (p.seq_lens ? p.seq_lens[b] : 0) + p.len_bias;
   return len < 0 ? 0 : len;
 }
+__device__ __forceinline__ int blocks_of(int len) { return (len + kBS - 1) / kBS; }
 
-// Walks the stage units of a CTA's range in order.
+// Position on the line of blocks: sequence b, sub-item (= kv_head*head_groups +
+// head_group), block blk of the sequence.  kvh and the block-table row of b are
+// kept alongside so the per-block path needs no division and no 64-bit multiply.
 struct Cursor {
-  int b, kvh, off, su, len;
+  int b, sub, blk, nblk, len, kvh;
+  const int32_t* row;  // block-table row of sequence b (nullptr: identity table)
+  __device__ __forceinline__ void refresh(const DecodeParams& p) {
+    kvh = sub / p.head_groups;
+    row = p.block_table ? p.block_table + int64_t(b) * p.max_blocks_per_seq : nullptr;
+  }
   __device__ __forceinline__ void locate(const DecodeParams& p, const int* prefix, int64_t u) {
-    // first i with Hkv*prefix[i] > u, then b = i-1
-    int lo = 0, hi = p.batch;
+    const int per_seq = p.num_kv_heads * p.head_groups;
+    int lo = 0, hi = p.batch;  // first b with prefix[b+1]*per_seq > u
     while (lo < hi) {
       int mid = (lo + hi) >> 1;
-      if (int64_t(prefix[mid + 1]) * p.num_kv_heads > u) hi = mid; else lo = mid + 1;
+      if (int64_t(prefix[mid + 1]) * per_seq > u) hi = mid; else lo = mid + 1;
     }
     b = lo;
-    su = prefix[b + 1] - prefix[b];
-    int64_t r = u - int64_t(prefix[b]) * p.num_kv_heads;
-    kvh = int(r / su);
-    off = int(r - int64_t(kvh) * su);
+    nblk = prefix[b + 1] - prefix[b];
+    int64_t r = u - int64_t(prefix[b]) * per_seq;
+    sub = int(r / nblk);
+    blk = int(r - int64_t(sub) * nblk);
     len = seq_len_of(p, b);
+    refresh(p);
   }
-  // returns true when the step left the current item
+  // one block forward; returns true when that left the current item
   __device__ __forceinline__ bool advance(const DecodeParams& p, const int* prefix) {
-    if (++off < su) return false;
-    off = 0;
-    if (++kvh == p.num_kv_heads) {
-      kvh = 0;
+    if (++blk < nblk) return false;
+    blk = 0;
+    if (++sub == p.num_kv_heads * p.head_groups) {
+      sub = 0;
       do { ++b; } while (b < p.batch && prefix[b + 1] == prefix[b]);
       if (b < p.batch) {
-        su = prefix[b + 1] - prefix[b];
+        nblk = prefix[b + 1] - prefix[b];
         len = seq_len_of(p, b);
       }
     }
+    if (b < p.batch) refresh(p);
     return true;
   }
 };
 
-__device__ __forceinline__ int64_t range_start(int64_t total, int c, int g) {
+__device__ __forceinline__ int64_t range_start(int64_t total, int64_t c, int64_t g) {
   return (total * c) / g;
 }
 
-// Sum-reduce N per-thread partials across the 8 lanes of a token group by
-// recursive halving: after the step with lane mask m a lane keeps the lower half
-// of its values if (sub & m) == 0, the upper half otherwise.  Leaves max(1, N/8)
-// finished values in v[0..].
-template <int N>
-__device__ __forceinline__ void reduce_scatter8(float* v, int sub) {
-  int n = N;
-#pragma unroll
-  for (int m = 4; m >= 1; m >>= 1) {
-    if (n >= 2) {
-      const int half = n / 2;
-      const bool upper = (sub & m) != 0;
-#pragma unroll
-      for (int i = 0; i < N / 2; ++i) {
-        if (i < half) {
-          float send = upper ? v[i] : v[i + half];
-          float keep = upper ? v[i + half] : v[i];
-          v[i] = keep + __shfl_xor_sync(0xffffffffu, send, m);
-        }
-      }
-      n = half;
-    } else {
-      v[0] += __shfl_xor_sync(0xffffffffu, v[0], m);
-    }
-  }
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-template <typename T, int QH, int HG>
-__global__ void __launch_bounds__(Cfg<T, QH, HG>::kThreads, Cfg<T, QH, HG>::kCtasPerSm)
+template <typename T, int QH, int NW, int NS>
+__global__ void __launch_bounds__(Cfg<T, QH, NW, NS>::kThreads, 1)
 paged_decode_kernel(const DecodeParams p) {
-  using C = Cfg<T, QH, HG>;
-  constexpr int E = Elt<T>::kPer16B;      // elements per 16-byte vector
-  constexpr int NCH = 16 / E;             // 16-byte chunks per thread per row (16 dims)
-  constexpr int NV = (4 * QH >= 8) ? (4 * QH / 8) : 1;  // finished scores per thread per block
+  using C = Cfg<T, QH, NW, NS>;
+  constexpr int E = Elt<T>::kPer16B;  // elements per 16-byte vector
+  constexpr int NCH = 16 / E;         // 16-byte chunks per thread per row (16 dims per thread)
+  constexpr int NV = (QH == 4) ? 2 : 1;  // finished scores per thread per block
   extern __shared__ __align__(128) uint8_t smem[];
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::kOffBars);
-  uint64_t* empty_bar = full_bar + C::kStages;
-  int* prefix = reinterpret_cast<int*>(smem + C::kOffPrefix);
-  int* abort_flag = prefix + kMaxBatch + 1;
-
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  const int G = gridDim.x, cta = blockIdx.x;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffBars) + warp * 2 * NS;  // K slots, V slots
+  int* prefix = reinterpret_cast<int*>(smem + C::kOffPrefix);
+  uint8_t* ring = smem + warp * C::kWarpRingB;
+  float* p_s = reinterpret_cast<float*>(smem + C::kOffP) + warp * (2 * kBS * 4);  // two buffers
 
-  // ---- set-up: stage-unit prefix over sequences, barriers ----
-  if (tid == 0) {
-    for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(full_bar + s, 1);
-      mbar_init(empty_bar + s, C::kConsumerWarps);
-    }
+  // ---- prologue: block prefix over sequences (whole CTA), this warp's barriers ----
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < 2 * NS; ++s) mbar_init(bars + s, 1);
     mbar_fence_init();
-    *abort_flag = 0;
   }
-  for (int b = tid; b < p.batch; b += C::kThreads) {
-    int len = seq_len_of(p, b);
-    prefix[b + 1] = (len + kBS * kBPS - 1) / (kBS * kBPS);
+  for (int b = tid; b < p.batch; b += C::kThreads) prefix[b + 1] = blocks_of(seq_len_of(p, b));
+  if (blockIdx.x == 0) {  // a sequence without tokens gets zeros (no warp ever visits it)
+    for (int b = 0; b < p.batch; ++b) {
+      if (seq_len_of(p, b) > 0) continue;
+      T* o = static_cast<T*>(p.out) + int64_t(b) * p.num_q_heads * kD;
+      for (int e = tid; e < p.num_q_heads * kD; e += C::kThreads) o[e] = Elt<T>::from_float(0.f);
+    }
   }
   if (tid == 0) prefix[0] = 0;
   __syncthreads();
-  if (warp == 0) {  // inclusive scan, one warp, chunks of 32
+  if (warp == 0) {  // inclusive scan in chunks of 32
     int carry = 0;
     for (int base = 0; base < p.batch; base += 32) {
       int i = base + lane;
@@ -183,124 +169,106 @@ paged_decode_kernel(const DecodeParams p) {
     }
   }
   __syncthreads();
-  const int64_t total_units = int64_t(prefix[p.batch]) * p.num_kv_heads;
-  const int64_t u0 = range_start(total_units, cta, G), u1 = range_start(total_units, cta + 1, G);
-  if (u0 >= u1) return;
-  const int n_units = int(u1 - u0);
+  const int64_t total = int64_t(prefix[p.batch]) * p.num_kv_heads * p.head_groups;
+  const int64_t W = int64_t(gridDim.x) * C::kWarps;
+  const int64_t worker = int64_t(blockIdx.x) * C::kWarps + warp;
+  const int64_t u0 = range_start(total, worker, W), u1 = range_start(total, worker + 1, W);
+  if (u0 >= u1) return;  // nothing below synchronises across warps
+  const int n = int(u1 - u0);
 
-  // ============================ producer role (warp 0) ============================
-  // Warp 0 doubles as the producer: after it has finished a stage it refills that
-  // slot with the unit kStages ahead.  Lanes 0..3 fetch the block ids of a unit one
-  // iteration before they are needed, so the table lookup is off the critical path.
-  Cursor pcur;            // next unit to issue
-  int p_next_id = -1;     // block id (lanes 0..3) of the unit at pcur
-  int p_issued = 0;       // units issued so far
-  auto load_id = [&](const Cursor& c) -> int {
-    int blk = c.off * kBPS + (lane & 3);
-    int nblk = (c.len + kBS - 1) / kBS;
-    if (lane >= kBPS || blk >= nblk) return -1;
-    int id = p.block_table ? p.block_table[int64_t(c.b) * p.max_blocks_per_seq + blk] : blk;
+  const int tg = lane >> 3;  // token group: tokens it*4 + tg
+  const int sub = lane & 7;  // owns 16 of the 128 dims
+  // Register r of the score pass holds token (r ^ perm)*4 + tg: the lane-dependent
+  // order lets the cross-lane halving below keep/send fixed registers.
+  const int perm = ((sub >> 2) & 1) * 2 + ((sub >> 1) & 1);
+  const int my_j0 = (QH == 4) ? (sub & 1) * 2 : (QH == 2 ? (sub & 1) : 0);
+  const bool hi_lane = (sub & 1) != 0;
+  // byte offset of this thread's chunk c inside a row of a tile
+  int coff[NCH];
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) coff[c] = (c * (kD / NCH) + sub * E) * C::kEltB;
+
+  // ---- producer side: block ids and bulk copies of this warp's own range ----
+  // One cursor walks the range NS blocks ahead of the consumer.  The K tile of a block
+  // is requested when a K slot frees up; its V tile is requested one step later (the
+  // output pass trails the score pass by one block), reusing the source offset and
+  // row count remembered from the K request.
+  Cursor pc;
+  pc.locate(p, prefix, u0);
+  int pc_id;            // block id at pc (loaded one step before it is needed)
+  int64_t last_off = 0; // byte offset of the last requested block's (block, kv head) tile
+  int last_rows = kBS;  // its number of existing rows (strided layout only)
+  int k_issued = 0, v_issued = 0;
+  auto load_id = [&]() -> int {
+    int id = pc.row ? __ldg(pc.row + pc.blk) : pc.blk;
     if (id < 0 || (p.num_blocks > 0 && id >= p.num_blocks)) {
-      atomicMax(p.status, KPX_ERR_INVALID_ARGUMENT);
+      if (lane == 0) atomicMax(p.status, KPX_ERR_INVALID_ARGUMENT);
       id = 0;
     }
     return id;
   };
-  // issue the copies of the unit at pcur into `slot` (the slot must be free), then
-  // step pcur and prefetch the ids of the following unit
-  auto issue_next = [&]() {
-    const int slot = p_issued % C::kStages;
-    const Cursor here = pcur;
-    const int my_id = p_next_id;
-    const int nblk = (here.len + kBS - 1) / kBS;
-    const int nb = min(kBPS, nblk - here.off * kBPS);
-    uint8_t* stage = smem + slot * C::kStageB;
+  // request one tile (callers have __syncwarp'ed after the last read of the slot)
+  auto copy_tile = [&](const uint8_t* pool, int64_t off, int rows, int slot_index) {
+    uint64_t* bar = bars + slot_index;
+    uint8_t* dst = ring + slot_index * C::kTileB;
     if (p.tile_contig) {
-      if (lane == 0) mbar_arrive_expect_tx(full_bar + slot, uint32_t(nb) * 2u * C::kTileB);
-      __syncwarp();
-      int blk = lane >> 1, which = lane & 1;  // lane -> (block, K/V)
-      int id = __shfl_sync(0xffffffffu, my_id, blk & 3);
-      if (lane < 2 * nb) {
-        const uint8_t* src = (which ? p.v_pool : p.k_pool) + int64_t(id) * p.block_stride_b +
-                             int64_t(here.kvh) * p.head_stride_b;
-        bulk_g2s(stage + which * (kBPS * C::kTileB) + blk * C::kTileB, src, C::kTileB,
-                 full_bar + slot);
+      if (lane == 0) {
+        mbar_arrive_expect_tx(bar, C::kTileB);
+        bulk_g2s(dst, pool + off, C::kTileB, bar);
       }
     } else {
-      // strided rows (the reference's token-major cache): one bulk copy per valid row
+      // strided rows (the reference's token-major cache): one bulk copy per existing row
       constexpr int kRowB = kD * C::kEltB;
-      int rows_total = min(here.len - here.off * kBPS * kBS, kBPS * kBS);
-      if (lane == 0) mbar_arrive_expect_tx(full_bar + slot, uint32_t(rows_total) * 2u * kRowB);
+      if (lane == 0) mbar_arrive_expect_tx(bar, uint32_t(rows) * kRowB);
       __syncwarp();
-      for (int c = lane; c < 2 * kBPS * kBS; c += 32) {
-        int blk = c >> 5, which = (c >> 4) & 1, row = c & 15;
-        int id = __shfl_sync(0xffffffffu, my_id, blk);
-        if (blk * kBS + row < rows_total) {
-          const uint8_t* src = (which ? p.v_pool : p.k_pool) + int64_t(id) * p.block_stride_b +
-                               int64_t(here.kvh) * p.head_stride_b + int64_t(row) * p.token_stride_b;
-          bulk_g2s(stage + which * (kBPS * C::kTileB) + blk * C::kTileB + row * kRowB, src, kRowB,
-                   full_bar + slot);
-        }
-      }
+      if (lane < rows) bulk_g2s(dst + lane * kRowB, pool + off + int64_t(lane) * p.token_stride_b, kRowB, bar);
     }
-    ++p_issued;
-    pcur.advance(p, prefix);
-    if (p_issued < n_units) p_next_id = load_id(pcur);
   };
-  if (warp == 0) {
-    pcur.locate(p, prefix, u0);
-    p_next_id = load_id(pcur);
-    const int pre = min(n_units, C::kStages);
-    for (int i = 0; i < pre; ++i) issue_next();
+  auto issue_k = [&](int slot) {  // K tile of the block at pc; then step pc
+    last_off = int64_t(pc_id) * p.block_stride_b + int64_t(pc.kvh) * p.head_stride_b;
+    last_rows = min(kBS, pc.len - pc.blk * kBS);
+    copy_tile(p.k_pool, last_off, last_rows, slot);
+    ++k_issued;
+    pc.advance(p, prefix);
+    if (k_issued < n) pc_id = load_id();
+  };
+  auto issue_v = [&](int slot) {  // V tile of the block whose K tile was requested last
+    copy_tile(p.v_pool, last_off, last_rows, NS + slot);
+    ++v_issued;
+  };
+  pc_id = load_id();
+#pragma unroll
+  for (int k = 0; k < NS; ++k) {
+    if (k < n) {
+      issue_k(k);
+      issue_v(k);
+    }
   }
 
-  // ================================ consumer warps =================================
-  const int hg = warp / kBPS;     // head group of this warp
-  const int wb = warp % kBPS;     // block of the stage this warp owns
-  const int tg = lane >> 3;       // token group 0..3: tokens it*4+tg
-  const int sub = lane & 7;       // 16 of the 128 dims
-  float* p_s = reinterpret_cast<float*>(smem + C::kOffP) + warp * (kBS * 4);
-  float* mg = reinterpret_cast<float*>(smem + C::kOffMerge) + hg * C::kMergeFloats;
-  float* mg_acc = mg;                       // [kBPS][QH][kD]
-  float* mg_m = mg + kBPS * QH * kD;        // [kBPS][QH]
-  float* mg_l = mg_m + kBPS * QH;           // [kBPS][QH]
-  const int gtid = tid - hg * (32 * kBPS);  // 0..127 inside the head group
-  const int bar_id = 1 + hg;
-
-  // element offset of this thread's chunk c inside a 128-wide row
-  auto chunk_off = [&](int c) -> int { return c * (kD / NCH) + sub * E; };
-
-  // which finished scores this thread ends up with after reduce_scatter8
-  int my_it, my_j0;
-  if (QH == 4) { my_it = ((sub >> 2) & 1) * 2 + ((sub >> 1) & 1); my_j0 = (sub & 1) * 2; }
-  else if (QH == 2) { my_it = sub >> 1; my_j0 = sub & 1; }
-  else { my_it = sub >> 1; my_j0 = 0; }
-
-  Cursor cur;
+  // ---- consumer state ----
+  Cursor cur;  // first block of the current segment
   cur.locate(p, prefix, u0);
-  bool aborted = false;
-
   float2 q2[QH][8];
   float2 acc[QH][8];
   float m_run[NV], l_run[NV];
 
   auto begin_item = [&]() {
+    const int hg = cur.sub - cur.kvh * p.head_groups;
     const T* qrow = static_cast<const T*>(p.q) + int64_t(cur.b) * p.num_q_heads * kD;
 #pragma unroll
     for (int j = 0; j < QH; ++j) {
-      int hq = hg * QH + j;
-      bool valid = hq < p.kv_mul;
+      const int hq = hg * QH + j;
+      const bool valid = hq < p.kv_mul;
       const T* qh = qrow + int64_t(cur.kvh * p.kv_mul + (valid ? hq : 0)) * kD;
+      const float sc = valid ? p.qscale : 0.f;
 #pragma unroll
       for (int c = 0; c < NCH; ++c) {
         float f[E];
-        uint4 raw = __ldg(reinterpret_cast<const uint4*>(qh + chunk_off(c)));
+        uint4 raw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(qh) + coff[c]));
         Elt<T>::unpack(raw, f);
 #pragma unroll
-        for (int e = 0; e < E; e += 2) {
-          float sc = valid ? p.qscale : 0.f;
+        for (int e = 0; e < E; e += 2)
           q2[j][(c * E + e) / 2] = make_float2(f[e] * sc, f[e + 1] * sc);
-        }
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[j][i] = make_float2(0.f, 0.f);
@@ -309,8 +277,44 @@ paged_decode_kernel(const DecodeParams p) {
     for (int k = 0; k < NV; ++k) { m_run[k] = -INFINITY; l_run[k] = 0.f; }
   };
 
-  auto end_item = [&](const Cursor& item, bool whole_item, int partial_slot) {
-    // reduce over the 4 token groups of the warp
+  // out += p * V for the block whose V tile is at vt and whose weights are in pb.
+  // kFull: all 16 tokens exist (no predicates).
+  auto pv_pass = [&](const uint8_t* vt, const float* pb, int nvalid, auto full_tag) {
+    constexpr bool kFull = decltype(full_tag)::value;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int tok = r * 4 + tg;
+      if (kFull || tok < nvalid) {
+        float vf[16];
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          uint4 raw = *reinterpret_cast<const uint4*>(vt + tok * (kD * C::kEltB) + coff[c]);
+          Elt<T>::unpack(raw, vf + c * E);
+        }
+        float pj[4];
+        if (QH == 4) {
+          float4 t4 = *reinterpret_cast<const float4*>(pb + tok * 4);
+          pj[0] = t4.x; pj[1] = t4.y; pj[2] = t4.z; pj[3] = t4.w;
+        } else if (QH == 2) {
+          float2 t2 = *reinterpret_cast<const float2*>(pb + tok * 4);
+          pj[0] = t2.x; pj[1] = t2.y;
+        } else {
+          pj[0] = pb[tok * 4];
+        }
+#pragma unroll
+        for (int j = 0; j < QH; ++j) {
+          const float2 pp = make_float2(pj[j], pj[j]);
+#pragma unroll
+          for (int d = 0; d < 8; ++d)
+            acc[j][d] = __ffma2_rn(pp, make_float2(vf[2 * d], vf[2 * d + 1]), acc[j][d]);
+        }
+      }
+    }
+  };
+
+  auto end_item = [&](const Cursor& item, bool whole_item, int64_t partial_slot, int64_t item_start) {
+    const int hg = item.sub - item.kvh * p.head_groups;
+    // totals over the 4 token groups (every lane ends with the sums of its 16 dims)
 #pragma unroll
     for (int j = 0; j < QH; ++j)
 #pragma unroll
@@ -322,6 +326,7 @@ paged_decode_kernel(const DecodeParams p) {
         a.y += __shfl_xor_sync(0xffffffffu, a.y, 16);
         acc[j][i] = a;
       }
+    float mh[QH], lh[QH];  // running max and sum of every head, in every lane
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       float l = l_run[k];
@@ -331,325 +336,337 @@ paged_decode_kernel(const DecodeParams p) {
       l += __shfl_xor_sync(0xffffffffu, l, 16);
       l_run[k] = l;
     }
-    if (tg == 0) {
-#pragma unroll
-      for (int j = 0; j < QH; ++j)
-#pragma unroll
-        for (int c = 0; c < NCH; ++c)
-#pragma unroll
-          for (int e = 0; e < E; e += 2) {
-            float2 a = acc[j][(c * E + e) / 2];
-            *reinterpret_cast<float2*>(mg_acc + (wb * QH + j) * kD + chunk_off(c) + e) = a;
-          }
-      // one lane per finished-score owner publishes m and l of its heads
-      bool owner = (QH == 4) ? (sub < 2) : (QH == 2 ? (sub < 2) : (sub == 0));
-      if (owner) {
-#pragma unroll
-        for (int k = 0; k < NV; ++k) {
-          mg_m[wb * QH + my_j0 + k] = m_run[k];
-          mg_l[wb * QH + my_j0 + k] = l_run[k];
-        }
-      }
+    if (QH == 4) {
+      float om0 = __shfl_xor_sync(0xffffffffu, m_run[0], 1), om1 = __shfl_xor_sync(0xffffffffu, m_run[NV - 1], 1);
+      float ol0 = __shfl_xor_sync(0xffffffffu, l_run[0], 1), ol1 = __shfl_xor_sync(0xffffffffu, l_run[NV - 1], 1);
+      mh[0] = hi_lane ? om0 : m_run[0];           lh[0] = hi_lane ? ol0 : l_run[0];
+      mh[1 % QH] = hi_lane ? om1 : m_run[NV - 1]; lh[1 % QH] = hi_lane ? ol1 : l_run[NV - 1];
+      mh[2 % QH] = hi_lane ? m_run[0] : om0;      lh[2 % QH] = hi_lane ? l_run[0] : ol0;
+      mh[3 % QH] = hi_lane ? m_run[NV - 1] : om1; lh[3 % QH] = hi_lane ? l_run[NV - 1] : ol1;
+    } else if (QH == 2) {
+      float om = __shfl_xor_sync(0xffffffffu, m_run[0], 1), ol = __shfl_xor_sync(0xffffffffu, l_run[0], 1);
+      mh[0] = hi_lane ? om : m_run[0];      lh[0] = hi_lane ? ol : l_run[0];
+      mh[1 % QH] = hi_lane ? m_run[0] : om; lh[1 % QH] = hi_lane ? l_run[0] : ol;
+    } else {
+      mh[0] = m_run[0];
+      lh[0] = l_run[0];
     }
-    named_bar_sync(bar_id, 32 * kBPS);
-    // combine the 4 warps: thread gtid owns dim gtid of every head
-    T* orow = static_cast<T*>(p.out) + int64_t(item.b) * p.num_q_heads * kD;
-    float* pslot = p.partials + int64_t(partial_slot) * C::kPartialFloats;
+    // token group tg writes head j == tg (all groups hold the same sums)
 #pragma unroll
     for (int j = 0; j < QH; ++j) {
-      int hq = hg * QH + j;
-      float M = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < kBPS; ++w) M = fmaxf(M, mg_m[w * QH + j]);
-      float L = 0.f, O = 0.f;
-#pragma unroll
-      for (int w = 0; w < kBPS; ++w) {
-        float mw = mg_m[w * QH + j];
-        float sc = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
-        L += mg_l[w * QH + j] * sc;
-        O += mg_acc[(w * QH + j) * kD + gtid] * sc;
-      }
-      if (hq < p.kv_mul) {
+      const int hq = hg * QH + j;
+      if (tg == (j & 3) && hq < p.kv_mul) {
         if (whole_item) {
-          orow[int64_t(item.kvh * p.kv_mul + hq) * kD + gtid] = Elt<T>::from_float(O / L);
+          uint8_t* o = reinterpret_cast<uint8_t*>(static_cast<T*>(p.out) + int64_t(item.b) * p.num_q_heads * kD +
+                                                  int64_t(item.kvh * p.kv_mul + hq) * kD);
+          const float inv = 1.f / lh[j];
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) {
+            __align__(16) T tmp[E];
+#pragma unroll
+            for (int e = 0; e < E; e += 2) {
+              float2 a = acc[j][(c * E + e) / 2];
+              tmp[e] = Elt<T>::from_float(a.x * inv);
+              tmp[e + 1] = Elt<T>::from_float(a.y * inv);
+            }
+            *reinterpret_cast<uint4*>(o + coff[c]) = *reinterpret_cast<const uint4*>(tmp);
+          }
         } else {
-          pslot[hq * kD + gtid] = O;
-          if (gtid == 0) {
-            pslot[HG * QH * kD + hq] = M;
-            pslot[HG * QH * kD + HG * QH + hq] = L;
+          float* ps = p.partials + partial_slot * C::kPartialFloats;
+#pragma unroll
+          for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int e = 0; e < E; e += 2)
+              *reinterpret_cast<float2*>(ps + j * kD + coff[c] / C::kEltB + e) = acc[j][(c * E + e) / 2];
+          if (sub == 0) {
+            ps[QH * kD + j] = mh[j];
+            ps[QH * kD + QH + j] = lh[j];
           }
         }
       }
     }
-    named_bar_sync(bar_id, 32 * kBPS);
+    if (whole_item) return;
+    // The item is cut by a range boundary.  Publish this piece, then count it; the warp
+    // that brings the count up to the number of pieces assembles the item from all of
+    // them (nobody waits: whoever arrives last does the work) and resets the counter.
+    __threadfence();
+    __syncwarp();
+    auto owner_of = [&](int64_t u) -> int64_t {
+      int64_t c = (u * W) / total;
+      if (c >= W) c = W - 1;
+      while (c + 1 < W && range_start(total, c + 1, W) <= u) ++c;
+      while (c > 0 && range_start(total, c, W) > u) --c;
+      return c;
+    };
+    const int64_t c_first = owner_of(item_start), c_last = owner_of(item_start + item.nblk - 1);
+    int pieces = 0;
+    for (int64_t c = c_first + lane; c <= c_last; c += 32)
+      pieces += range_start(total, c, W) < range_start(total, c + 1, W) ? 1 : 0;
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) pieces += __shfl_xor_sync(0xffffffffu, pieces, d);
+    int* cnt = p.counters + (item.b * (p.num_kv_heads * p.head_groups) + item.sub);
+    int prev = 0;
+    if (lane == 0) prev = atomicAdd(cnt, 1);
+    prev = __shfl_sync(0xffffffffu, prev, 0);
+    if (prev != pieces - 1) return;
+    if (lane == 0) *cnt = 0;
+    __threadfence();
+    const int j = tg;  // token group tg assembles head tg; lane `sub` its 16 dims
+    const int hq = hg * QH + j;
+    if (j < QH && hq < p.kv_mul) {
+      float M = -INFINITY, L = 0.f;
+      float O[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) O[e] = 0.f;
+#pragma unroll 2
+      for (int64_t c = c_first; c <= c_last; ++c) {
+        const int64_t cs = range_start(total, c, W);
+        if (cs >= range_start(total, c + 1, W)) continue;  // that warp had no blocks
+        const float* ps = p.partials + ((item_start < cs) ? 2 * c : 2 * c + 1) * C::kPartialFloats;
+        const float mw = __ldcg(ps + QH * kD + j), lw = __ldcg(ps + QH * kD + QH + j);
+        float4 v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          v[k] = __ldcg(reinterpret_cast<const float4*>(ps + j * kD + coff[(k * 4) / E] / C::kEltB + (k * 4) % E));
+        const float Mn = fmaxf(M, mw);
+        const float a = fast_exp2(M - Mn), bsc = fast_exp2(mw - Mn);
+        L = L * a + lw * bsc;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          O[4 * k + 0] = O[4 * k + 0] * a + v[k].x * bsc;
+          O[4 * k + 1] = O[4 * k + 1] * a + v[k].y * bsc;
+          O[4 * k + 2] = O[4 * k + 2] * a + v[k].z * bsc;
+          O[4 * k + 3] = O[4 * k + 3] * a + v[k].w * bsc;
+        }
+        M = Mn;
+      }
+      uint8_t* o = reinterpret_cast<uint8_t*>(static_cast<T*>(p.out) + int64_t(item.b) * p.num_q_heads * kD +
+                                              int64_t(item.kvh * p.kv_mul + hq) * kD);
+      const float inv = 1.f / L;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        __align__(16) T tmp[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) tmp[e] = Elt<T>::from_float(O[c * E + e] * inv);
+        *reinterpret_cast<uint4*>(o + coff[c]) = *reinterpret_cast<const uint4*>(tmp);
+      }
+    }
+  };
+
+  auto wait_slot = [&](uint64_t* bar, uint32_t ph) -> bool {
+    if (mbar_try_wait(bar, ph)) return true;
+    bool ok = mbar_wait_bounded(bar, ph);
+    if (!__all_sync(0xffffffffu, ok)) {
+      if (lane == 0) atomicMax(p.status, KPX_ERR_DEVICE_TIMEOUT);
+      return false;
+    }
+    return true;
   };
 
   begin_item();
-  int64_t item_first_unit = u0 - cur.off;  // global unit index where the current item starts
-  for (int it = 0; it < n_units; ++it) {
-    const int slot = it % C::kStages;
-    if (!aborted) {
-      if (!mbar_wait_bounded(full_bar + slot, (it / C::kStages) & 1)) {
-        aborted = true;
-        *reinterpret_cast<volatile int*>(abort_flag) = 1;
-        atomicMax(p.status, KPX_ERR_DEVICE_TIMEOUT);
-      }
+  int64_t item_first = u0 - cur.blk;  // global block index where the current item starts
+  int ks = 0, vs = 0;                 // slots of the next K block and the next V block to consume
+  uint32_t kph = 0, vph = 0;          // their phase parities
+
+  // One iteration: scores + online softmax of block i; when kPend, the output pass of
+  // block i-1 sits in the same straight-line region as the shuffle chains so that its
+  // loads and FMAs fill their latency.  Returns false if a bounded wait gave up.
+  auto step = [&](int i, int nvalid, auto pend_tag) -> bool {
+    constexpr bool kPend = decltype(pend_tag)::value;
+    if (!wait_slot(bars + ks, kph)) return false;
+    if (kPend) {
+      if (!wait_slot(bars + NS + vs, vph)) return false;
     }
-    aborted = __any_sync(0xffffffffu, aborted || *reinterpret_cast<volatile int*>(abort_flag) != 0);
-    const int blk = cur.off * kBPS + wb;
-    const int nvalid = cur.len - blk * kBS;  // tokens of this block that exist (may be <= 0)
-    if (!aborted && nvalid > 0) {
-      const uint8_t* kt = smem + slot * C::kStageB + wb * C::kTileB;
-      const uint8_t* vt = kt + kBPS * C::kTileB;
-      // ---- scores: s[it][j] partial over this thread's 16 dims ----
-      float part[4 * QH];
+    float part[4 * QH];
+    {
+      const uint8_t* kt = ring + ks * C::kTileB;
 #pragma unroll
-      for (int i4 = 0; i4 < 4; ++i4) {
-        const int tok = i4 * 4 + tg;
+      for (int r = 0; r < 4; ++r) {
+        const uint8_t* krow = kt + ((r ^ perm) * 4 + tg) * (kD * C::kEltB);
         float kf[16];
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
-          uint4 raw = *reinterpret_cast<const uint4*>(kt + (tok * kD + chunk_off(c)) * C::kEltB);
+          uint4 raw = *reinterpret_cast<const uint4*>(krow + coff[c]);
           Elt<T>::unpack(raw, kf + c * E);
         }
 #pragma unroll
         for (int j = 0; j < QH; ++j) {
           float2 s2 = make_float2(0.f, 0.f);
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            s2 = __ffma2_rn(q2[j][i], make_float2(kf[2 * i], kf[2 * i + 1]), s2);
-          part[i4 * QH + j] = s2.x + s2.y;
+          for (int d = 0; d < 8; ++d)
+            s2 = __ffma2_rn(q2[j][d], make_float2(kf[2 * d], kf[2 * d + 1]), s2);
+          part[r * QH + j] = s2.x + s2.y;
         }
       }
-      reduce_scatter8<4 * QH>(part, sub);
-      // ---- online softmax on this thread's NV finished scores (token my_it*4+tg) ----
-      const bool tok_ok = (my_it * 4 + tg) < nvalid;
-      float alpha[NV];
-      bool changed = false;
+    }
+    // halving: registers r>=2 go to lane^4, then r==1 to lane^2; what is left is token perm*4+tg
 #pragma unroll
-      for (int k = 0; k < NV; ++k) {
-        float s = tok_ok ? part[k] : -INFINITY;
-        float mx = s;
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-        float m_new = fmaxf(m_run[k], mx);
-        alpha[k] = fast_exp2(m_run[k] - m_new);
-        changed |= (m_new != m_run[k]);
-        m_run[k] = m_new;
-        float pv = fast_exp2(s - m_new);
-        l_run[k] = l_run[k] * alpha[k] + pv;
-        part[k] = pv;
-      }
+    for (int k = 0; k < 2 * QH; ++k) part[k] += __shfl_xor_sync(0xffffffffu, part[2 * QH + k], 4);
+#pragma unroll
+    for (int k = 0; k < QH; ++k) part[k] += __shfl_xor_sync(0xffffffffu, part[QH + k], 2);
+    if (QH == 4) {
+      float s0 = hi_lane ? part[0] : part[2], s1 = hi_lane ? part[1] : part[3];
+      float k0 = hi_lane ? part[2] : part[0], k1 = hi_lane ? part[3] : part[1];
+      part[0] = k0 + __shfl_xor_sync(0xffffffffu, s0, 1);
+      part[1] = k1 + __shfl_xor_sync(0xffffffffu, s1, 1);
+    } else if (QH == 2) {
+      float s0 = hi_lane ? part[0] : part[1], k0 = hi_lane ? part[1] : part[0];
+      part[0] = k0 + __shfl_xor_sync(0xffffffffu, s0, 1);
+    } else {
+      part[0] += __shfl_xor_sync(0xffffffffu, part[0], 1);
+    }
+    const bool tok_ok = (perm * 4 + tg) < nvalid;
+    float alpha[NV];
+    bool changed = false;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      float sc = tok_ok ? part[k] : -INFINITY;
+      float mx = sc;
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      const float m_new = fmaxf(m_run[k], mx);
+      alpha[k] = fast_exp2(m_run[k] - m_new);
+      changed |= (m_new != m_run[k]);
+      m_run[k] = m_new;
+      const float pw = fast_exp2(sc - m_new);
+      l_run[k] = l_run[k] * alpha[k] + pw;
+      part[k] = pw;
+    }
+    if (kPend)
+      pv_pass(ring + (NS + vs) * C::kTileB, p_s + ((i - 1) & 1) * (kBS * 4), kBS, std::true_type{});
+    float* pb_new = p_s + (i & 1) * (kBS * 4);
+    if (QH == 4) {
+      *reinterpret_cast<float2*>(pb_new + (perm * 4 + tg) * 4 + my_j0) = make_float2(part[0], part[1]);
+    } else {
+      pb_new[(perm * 4 + tg) * 4 + my_j0] = part[0];
+    }
+    if (__any_sync(0xffffffffu, changed)) {
+      float al[QH];
       if (QH == 4) {
-        *reinterpret_cast<float2*>(p_s + (my_it * 4 + tg) * 4 + my_j0) = make_float2(part[0], part[1]);
+        float o0 = __shfl_xor_sync(0xffffffffu, alpha[0], 1);
+        float o1 = __shfl_xor_sync(0xffffffffu, alpha[NV - 1], 1);
+        al[0] = hi_lane ? o0 : alpha[0];
+        al[1 % QH] = hi_lane ? o1 : alpha[NV - 1];
+        al[2 % QH] = hi_lane ? alpha[0] : o0;
+        al[3 % QH] = hi_lane ? alpha[NV - 1] : o1;
+      } else if (QH == 2) {
+        float o0 = __shfl_xor_sync(0xffffffffu, alpha[0], 1);
+        al[0] = hi_lane ? o0 : alpha[0];
+        al[1 % QH] = hi_lane ? alpha[0] : o0;
       } else {
-        p_s[(my_it * 4 + tg) * 4 + my_j0] = part[0];
+        al[0] = alpha[0];
       }
-      if (__any_sync(0xffffffffu, changed)) {
-        // rescale the accumulators of every head; fetch the other lanes' factors
-        float al[QH];
-        if (QH == 4) {
-          float o0 = __shfl_xor_sync(0xffffffffu, alpha[0], 1);
-          float o1 = __shfl_xor_sync(0xffffffffu, alpha[NV - 1], 1);
-          bool hi = (sub & 1) != 0;
-          al[0] = hi ? o0 : alpha[0];
-          al[1] = hi ? o1 : alpha[NV - 1];
-          al[2 % QH] = hi ? alpha[0] : o0;
-          al[3 % QH] = hi ? alpha[NV - 1] : o1;
-        } else if (QH == 2) {
-          float o0 = __shfl_xor_sync(0xffffffffu, alpha[0], 1);
-          bool hi = (sub & 1) != 0;
-          al[0] = hi ? o0 : alpha[0];
-          al[1 % QH] = hi ? alpha[0] : o0;
-        } else {
-          al[0] = alpha[0];
+#pragma unroll
+      for (int j = 0; j < QH; ++j)
+#pragma unroll
+        for (int d = 0; d < 8; ++d) {
+          acc[j][d].x *= al[j];
+          acc[j][d].y *= al[j];
         }
-#pragma unroll
-        for (int j = 0; j < QH; ++j)
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            acc[j][i].x *= al[j];
-            acc[j][i].y *= al[j];
-          }
-      }
-      __syncwarp();
-      // ---- out += p * V ----
-#pragma unroll
-      for (int i4 = 0; i4 < 4; ++i4) {
-        const int tok = i4 * 4 + tg;
-        if (tok < nvalid) {
-          float vf[16];
-#pragma unroll
-          for (int c = 0; c < NCH; ++c) {
-            uint4 raw = *reinterpret_cast<const uint4*>(vt + (tok * kD + chunk_off(c)) * C::kEltB);
-            Elt<T>::unpack(raw, vf + c * E);
-          }
-          float pj[4];
-          if (QH == 4) {
-            float4 t4 = *reinterpret_cast<const float4*>(p_s + tok * 4);
-            pj[0] = t4.x; pj[1] = t4.y; pj[2] = t4.z; pj[3] = t4.w;
-          } else if (QH == 2) {
-            float2 t2 = *reinterpret_cast<const float2*>(p_s + tok * 4);
-            pj[0] = t2.x; pj[1] = t2.y;
-          } else {
-            pj[0] = p_s[tok * 4];
-          }
-#pragma unroll
-          for (int j = 0; j < QH; ++j) {
-            float2 pp = make_float2(pj[j], pj[j]);
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              acc[j][i] = __ffma2_rn(pp, make_float2(vf[2 * i], vf[2 * i + 1]), acc[j][i]);
-          }
-        }
-      }
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(empty_bar + slot);
-    if (warp == 0 && p_issued < n_units) {
-      // refill this slot once all consumer warps have released it
-      if (!aborted && !mbar_wait_bounded(empty_bar + slot, (it / C::kStages) & 1)) {
-        aborted = true;
-        *reinterpret_cast<volatile int*>(abort_flag) = 1;
-        atomicMax(p.status, KPX_ERR_DEVICE_TIMEOUT);
-      }
-      aborted = __any_sync(0xffffffffu, aborted);
-      if (!aborted) issue_next();
+    __syncwarp();  // K(i) and V(i-1) fully read; p(i) visible to the whole warp
+    // ---------------- refill the slots just left ----------------
+    if (lane == 0) fence_proxy_async();
+    if (kPend) {
+      if (v_issued < n) issue_v(vs);
+      if (++vs == NS) { vs = 0; vph ^= 1; }
     }
-
-    const Cursor item = cur;
-    const bool left = cur.advance(p, prefix);
-    const bool last = (it + 1 == n_units);
-    if (left || last) {
-      const int64_t item_end = item_first_unit + item.su;
-      const bool whole = (item_first_unit >= u0) && (item_end <= u1);
-      const int pslot = (item_first_unit < u0) ? 2 * cta : 2 * cta + 1;
-      end_item(item, whole, pslot);
-      if (!last) {
-        item_first_unit = item_end;
-        begin_item();
-      }
-    }
-  }
-}
-
-// Second pass: items cut by a CTA range boundary are assembled from the partials
-// of the CTAs that touched them; empty sequences get zeros.  One CTA per
-// (sequence, kv head), one thread per output dim.
-template <typename T>
-__global__ void __launch_bounds__(kD) decode_merge_kernel(const DecodeParams p, int G, int slot_floats,
-                                                          int hq_total) {
-  __shared__ int s_prefix_b, s_su;
-  const int item = blockIdx.x;
-  const int b = item / p.num_kv_heads, kvh = item - b * p.num_kv_heads;
-  const int tid = threadIdx.x;
-  // stage-unit prefix of this sequence (batch is small: a serial scan by one warp is enough)
-  if (tid < 32) {
-    int64_t acc = 0, tot = 0;
-    for (int base = 0; base < p.batch; base += 32) {
-      int i = base + tid;
-      int su = 0;
-      if (i < p.batch) su = (seq_len_of(p, i) + kBS * kBPS - 1) / (kBS * kBPS);
-      int before = (i < b) ? su : 0;
-#pragma unroll
-      for (int d = 16; d >= 1; d >>= 1) {
-        before += __shfl_xor_sync(0xffffffffu, before, d);
-        su += __shfl_xor_sync(0xffffffffu, su, d);
-      }
-      acc += before;
-      tot += su;
-    }
-    if (tid == 0) {
-      s_prefix_b = int(acc);
-      s_su = int(tot);
-    }
-  }
-  __syncthreads();
-  const int su_b = (seq_len_of(p, b) + kBS * kBPS - 1) / (kBS * kBPS);
-  T* orow = static_cast<T*>(p.out) + int64_t(b) * p.num_q_heads * kD + int64_t(kvh) * p.kv_mul * kD;
-  if (su_b == 0) {
-    for (int h = 0; h < p.kv_mul; ++h) orow[h * kD + tid] = Elt<T>::from_float(0.f);
-    return;
-  }
-  const int64_t total = int64_t(s_su) * p.num_kv_heads;
-  const int64_t s_i = int64_t(s_prefix_b) * p.num_kv_heads + int64_t(kvh) * su_b;
-  const int64_t e_i = s_i + su_b;
-  auto owner_of = [&](int64_t u) -> int {
-    int c = int((u * G) / total);
-    if (c >= G) c = G - 1;
-    while (c + 1 < G && range_start(total, c + 1, G) <= u) ++c;
-    while (c > 0 && range_start(total, c, G) > u) --c;
-    return c;
+    if (k_issued < n) issue_k(ks);
+    if (++ks == NS) { ks = 0; kph ^= 1; }
+    return true;
   };
-  const int c_first = owner_of(s_i), c_last = owner_of(e_i - 1);
-  if (c_first == c_last) return;  // written directly by its only CTA
-  for (int h = 0; h < p.kv_mul; ++h) {
-    float M = -INFINITY;
-    for (int c = c_first; c <= c_last; ++c) {
-      if (range_start(total, c, G) >= range_start(total, c + 1, G)) continue;  // CTA had no units
-      int slot = (s_i < range_start(total, c, G)) ? 2 * c : 2 * c + 1;
-      M = fmaxf(M, p.partials[int64_t(slot) * slot_floats + hq_total * kD + h]);
+
+  // The range is a sequence of segments, each the part of one item that falls in it.
+  int i = 0;
+  while (i < n) {
+    const int m = min(n - i, cur.nblk - cur.blk);           // blocks of this item in the range
+    const bool to_item_end = (cur.blk + m == cur.nblk);
+    const int tail_valid = to_item_end ? cur.len - (cur.nblk - 1) * kBS : kBS;  // tokens in the segment's last block
+    if (!step(i, m == 1 ? tail_valid : kBS, std::false_type{})) return;
+    for (int t = 1; t < m; ++t)
+      if (!step(i + t, t == m - 1 ? tail_valid : kBS, std::true_type{})) return;
+    i += m;
+    // flush: output pass of the segment's last block (possibly a partial block)
+    if (!wait_slot(bars + NS + vs, vph)) return;
+    pv_pass(ring + (NS + vs) * C::kTileB, p_s + ((i - 1) & 1) * (kBS * 4), tail_valid, std::false_type{});
+    __syncwarp();
+    if (lane == 0) fence_proxy_async();
+    if (v_issued < n) issue_v(vs);
+    if (++vs == NS) { vs = 0; vph ^= 1; }
+    const int64_t item_end = item_first + cur.nblk;
+    const bool whole = (item_first >= u0) && (item_end <= u1);
+    const int64_t pslot = (item_first < u0) ? 2 * worker : 2 * worker + 1;
+    end_item(cur, whole, pslot, item_first);
+    if (i < n) {
+      cur.blk += m - 1;
+      cur.advance(p, prefix);
+      item_first = item_end;
+      begin_item();
     }
-    float L = 0.f, O = 0.f;
-    for (int c = c_first; c <= c_last; ++c) {
-      if (range_start(total, c, G) >= range_start(total, c + 1, G)) continue;
-      int slot = (s_i < range_start(total, c, G)) ? 2 * c : 2 * c + 1;
-      const float* ps = p.partials + int64_t(slot) * slot_floats;
-      float mw = ps[hq_total * kD + h];
-      float sc = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
-      L += ps[hq_total * kD + hq_total + h] * sc;
-      O += ps[h * kD + tid] * sc;
-    }
-    orow[h * kD + tid] = Elt<T>::from_float(O / L);
   }
 }
 
-struct DecodePlan {
-  int qh = 0, hg = 0;
-};
-inline bool plan_for(int kv_mul, DecodePlan* pl) {
-  if (kv_mul < 1 || kv_mul > 8) return false;
-  if (kv_mul == 1) { pl->qh = 1; pl->hg = 1; }
-  else if (kv_mul == 2) { pl->qh = 2; pl->hg = 1; }
-  else if (kv_mul <= 4) { pl->qh = 4; pl->hg = 1; }
-  else { pl->qh = 4; pl->hg = 2; }
-  return true;
+inline int heads_per_warp(int kv_mul);
+inline int64_t counter_bytes(int num_q_heads, int num_kv_heads) {
+  const int kv_mul = num_q_heads / num_kv_heads;
+  const int qh = heads_per_warp(kv_mul);
+  const int64_t items = int64_t(kMaxBatch) * num_kv_heads * ((kv_mul + qh - 1) / qh);
+  return (items * 4 + 255) / 256 * 256;
+}
+inline int heads_per_warp(int kv_mul) {
+  if (kv_mul == 1) return 1;
+  if (kv_mul == 2) return 2;
+  return 4;
 }
 
-constexpr int kMaxGrid = 148 * 2 * 2;  // upper bound used to size the workspace
+constexpr int kMaxSms = 160;  // upper bound used to size the workspace
+constexpr int kMaxWarpsPerCta = 16;
 constexpr int kStatusBytes = 256;
 
-template <typename T, int QH, int HG>
-int launch_decode(const DecodeParams& p, cudaStream_t stream, int* grid_out) {
-  using C = Cfg<T, QH, HG>;
+// Tuning knob: 0 = default shape; set through kpx_internal_set_decode_variant.
+int g_decode_variant = 0;
+
+template <typename T, int QH, int NW, int NS>
+int launch_decode(DecodeParams p, cudaStream_t stream) {
+  using C = Cfg<T, QH, NW, NS>;
   static int configured_dev = -1;
   int dev = 0;
   KPX_CUDA_TRY(cudaGetDevice(&dev));
-  auto kern = paged_decode_kernel<T, QH, HG>;
+  auto kern = paged_decode_kernel<T, QH, NW, NS>;
   if (configured_dev != dev) {
     KPX_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
     configured_dev = dev;
   }
-  int grid = device_info().sm_count * C::kCtasPerSm;
-  if (grid > kMaxGrid) grid = kMaxGrid;
-  *grid_out = grid;
+  int grid = device_info().sm_count;
+  if (grid > kMaxSms) grid = kMaxSms;
+  p.head_groups = (p.kv_mul + QH - 1) / QH;
   kern<<<grid, C::kThreads, C::kSmem, stream>>>(p);
   KPX_CUDA_TRY(cudaGetLastError());
-  decode_merge_kernel<T><<<p.batch * p.num_kv_heads, kD, 0, stream>>>(p, grid, C::kPartialFloats,
-                                                                      HG * QH);
   return cuda_status(cudaGetLastError());
 }
 
-template <typename T>
-int dispatch_decode(const DecodeParams& p, const DecodePlan& pl, cudaStream_t stream, int* grid) {
-  if (pl.hg == 1) {
-    if (pl.qh == 1) return launch_decode<T, 1, 1>(p, stream, grid);
-    if (pl.qh == 2) return launch_decode<T, 2, 1>(p, stream, grid);
-    return launch_decode<T, 4, 1>(p, stream, grid);
+template <typename T, int QH>
+int launch_shape(const DecodeParams& p, cudaStream_t stream) {
+  if (sizeof(T) == 4) return launch_decode<T, QH, 6, 2>(p, stream);
+  if (sizeof(T) == 2) {
+    switch (g_decode_variant) {
+      case 1: return launch_decode<T, QH, 8, 2>(p, stream);
+      case 2: return launch_decode<T, QH, 12, 2>(p, stream);
+      default: break;
+    }
   }
-  return launch_decode<T, 4, 2>(p, stream, grid);
+  return launch_decode<T, QH, 8, 3>(p, stream);
+}
+
+template <typename T>
+int dispatch_decode(const DecodeParams& p, cudaStream_t stream) {
+  switch (heads_per_warp(p.kv_mul)) {
+    case 1: return launch_shape<T, 1>(p, stream);
+    case 2: return launch_shape<T, 2>(p, stream);
+    default: return launch_shape<T, 4>(p, stream);
+  }
 }
 
 }  // namespace
@@ -657,13 +674,19 @@ int dispatch_decode(const DecodeParams& p, const DecodePlan& pl, cudaStream_t st
 
 using namespace kpx;
 
+extern "C" __attribute__((visibility("default"))) void kpx_internal_set_decode_variant(int v) {
+  g_decode_variant = v;
+}
+
 extern "C" int64_t kpx_decode_workspace_bytes(int32_t batch, int32_t num_q_heads,
                                               int32_t num_kv_heads, int32_t head_size) {
   (void)batch;
   if (num_q_heads <= 0 || num_kv_heads <= 0 || head_size != kD || num_q_heads % num_kv_heads)
     return -1;
-  // 2 partial slots per persistent CTA, each 8 heads x (128 + 2) floats at most
-  return int64_t(kStatusBytes) + int64_t(2) * kMaxGrid * 8 * (kD + 2) * sizeof(float);
+  // header + one counter per item of a launch + 2 partial slots per persistent warp,
+  // each up to 4 heads x (128 + 2) floats
+  return int64_t(kStatusBytes) + counter_bytes(num_q_heads, num_kv_heads) +
+         int64_t(2) * kMaxSms * kMaxWarpsPerCta * (4 * kD + 8) * sizeof(float);
 }
 
 extern "C" int kpx_paged_decode(void* out, const void* q, const void* k_pool, const void* v_pool,
@@ -675,10 +698,9 @@ extern "C" int kpx_paged_decode(void* out, const void* q, const void* k_pool, co
     return KPX_ERR_INVALID_ARGUMENT;
   if (layout->head_size != kD || layout->block_size != kBS) return KPX_ERR_UNIMPLEMENTED;
   if (num_q_heads % layout->num_kv_heads) return KPX_ERR_INVALID_ARGUMENT;
+  if (num_q_heads / layout->num_kv_heads > 64) return KPX_ERR_UNIMPLEMENTED;
   if (block_table && max_blocks_per_seq <= 0) return KPX_ERR_INVALID_ARGUMENT;
   if (!seq_lens && len_bias < 0) return KPX_ERR_INVALID_ARGUMENT;
-  DecodePlan pl;
-  if (!plan_for(num_q_heads / layout->num_kv_heads, &pl)) return KPX_ERR_UNIMPLEMENTED;
   if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15)) return KPX_ERR_INVALID_ARGUMENT;
   if ((reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool) |
        reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 15)
@@ -694,7 +716,9 @@ extern "C" int kpx_paged_decode(void* out, const void* q, const void* k_pool, co
   p.k_pool = static_cast<const uint8_t*>(k_pool);
   p.v_pool = static_cast<const uint8_t*>(v_pool);
   p.status = static_cast<int32_t*>(workspace);
-  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kStatusBytes);
+  p.counters = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(workspace) + kStatusBytes);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kStatusBytes +
+                                        counter_bytes(num_q_heads, layout->num_kv_heads));
   p.block_stride_b = layout->block_stride * eb;
   p.head_stride_b = layout->head_stride * eb;
   p.token_stride_b = layout->token_stride * eb;
@@ -704,9 +728,10 @@ extern "C" int kpx_paged_decode(void* out, const void* q, const void* k_pool, co
   p.num_q_heads = num_q_heads;
   p.num_kv_heads = layout->num_kv_heads;
   p.kv_mul = num_q_heads / layout->num_kv_heads;
+  p.head_groups = 1;
   p.tile_contig = tile_contiguous(layout) ? 1 : 0;
   p.qscale = scale * kLog2e;
-  // the prefix table of one launch lives in shared memory: long batches go in slices
+  // the block prefix of one launch lives in shared memory: long batches go in slices
   for (int32_t b0 = 0; b0 < batch; b0 += kMaxBatch) {
     int32_t nb = batch - b0 < kMaxBatch ? batch - b0 : kMaxBatch;
     p.batch = nb;
@@ -714,14 +739,13 @@ extern "C" int kpx_paged_decode(void* out, const void* q, const void* k_pool, co
     p.q = static_cast<const uint8_t*>(q) + int64_t(b0) * num_q_heads * kD * eb;
     p.block_table = block_table ? block_table + int64_t(b0) * max_blocks_per_seq : nullptr;
     p.seq_lens = seq_lens ? seq_lens + b0 : nullptr;
-    int grid = 0, rc;
+    int rc;
     switch (layout->dtype) {
-      case KPX_F16: rc = dispatch_decode<__half>(p, pl, s, &grid); break;
-      case KPX_BF16: rc = dispatch_decode<__nv_bfloat16>(p, pl, s, &grid); break;
-      default: rc = dispatch_decode<float>(p, pl, s, &grid); break;
+      case KPX_F16: rc = dispatch_decode<__half>(p, s); break;
+      case KPX_BF16: rc = dispatch_decode<__nv_bfloat16>(p, s); break;
+      default: rc = dispatch_decode<float>(p, s); break;
     }
     if (rc != KPX_OK) return rc;
   }
   return KPX_OK;
 }
-
