@@ -1,0 +1,402 @@
+#!/usr/bin/env python
+"""Headline benchmark: paged GQA decode attention at the Qwen3-8B attention shape.
+
+Workload (BASELINE.json configs[1]): 32 Q heads, 8 KV heads, head_dim 128, fp16 KV, block
+size 16, batch 64, per-sequence context lengths uniform in [128, 4096] from a seed, block
+pool = total blocks x 1.25 with a seeded random block table, Q/K/V ~ N(0,1).  One step =
+one decode step of the KV-cache hot path over all 36 layers: per layer, RoPE the new Q/K
+token of every sequence, append K/V into that layer's pool, then attend over the whole
+context through the block table.  Every layer has its own 0.66 GB pool, so consecutive
+launches never find their input in L2.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Prints ONE JSON line (rank 0).  `value` is KV-read GB/s (algorithmic bytes / device time,
+whole job); `e2e` is the same metric with the step's Q/K/V rows coming from pinned host
+memory and the attention output going back to the host inside the timed region.
+`--impl reference` times the CPU restatement of the reference's fp32 MHA path (the oracle,
+all host threads) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+Q_HEADS, KV_HEADS, HEAD, BLOCK = 32, 8, 128, 16
+BATCH, CTX_LO, CTX_HI, LAYERS = 64, 128, 4096, 36
+ROPE_THETA = 1e6
+SEED = 2024
+METRIC = "paged decode attn KV-read HBM GB/s"
+
+
+def peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        d = json.loads(f.read_text())
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def make_lens(seed, batch=BATCH):
+    rng = np.random.default_rng(seed)
+    return rng.integers(CTX_LO, CTX_HI + 1, size=batch).astype(np.int32)
+
+
+def kv_bytes_per_layer(lens_after_append):
+    """Algorithmic KV bytes one decode launch must read: every cached token's K and V row."""
+    return int(np.sum(lens_after_append)) * KV_HEADS * HEAD * 2 * 2
+
+
+class ClockSampler(threading.Thread):
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.rows, self._halt = index, [], threading.Event()
+
+    def run(self):
+        while not self._halt.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True,
+                                     timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            self._halt.wait(0.05)
+
+    def stop(self):
+        self._halt.set()
+        self.join(timeout=6)
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for k, n in enumerate(names) if any(len(r) > 3 + k and r[3 + k].lower() == "active" for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+class DecodeWorkload:
+    """Per-GPU state of the headline workload, resident in HBM."""
+
+    def __init__(self, rank, total_steps, device):
+        import torch
+        from orinmllm_b200 import capi
+        self.torch, self.capi, self.dev = torch, capi, device
+        self.lens0 = make_lens(SEED + 1000 * rank)
+        rng = np.random.default_rng(SEED + 1000 * rank + 1)
+        final = self.lens0 + total_steps
+        nblk = (final + BLOCK - 1) // BLOCK
+        self.num_blocks = int(np.ceil(int(nblk.sum()) * 1.25))
+        perm = rng.permutation(self.num_blocks).astype(np.int32)
+        self.max_blocks = int(nblk.max())
+        table = np.full((BATCH, self.max_blocks), -1, np.int32)
+        c = 0
+        for i, n in enumerate(nblk):
+            table[i, :n] = perm[c:c + n]
+            c += n
+        steps = np.arange(total_steps, dtype=np.int64)
+        pos = self.lens0[None, :].astype(np.int64) + steps[:, None]             # [T, B]
+        blk = table[np.arange(BATCH)[None, :], pos // BLOCK].astype(np.int64)
+        self.table = torch.from_numpy(table).to(device)
+        self.slots = torch.from_numpy(blk * BLOCK + pos % BLOCK).to(device)     # [T, B] int64
+        self.positions = torch.from_numpy(pos.astype(np.int32)).to(device)      # [T, B] int32
+        self.layout = capi.layout_paged(capi.KPX_F16, KV_HEADS, HEAD, BLOCK, self.num_blocks)
+        g = torch.Generator(device=device)
+        g.manual_seed(SEED + rank)
+        shape = (LAYERS, self.num_blocks, KV_HEADS, BLOCK, HEAD)
+        self.k_pool = torch.empty(shape, dtype=torch.float16, device=device)
+        self.v_pool = torch.empty(shape, dtype=torch.float16, device=device)
+        for l in range(LAYERS):
+            self.k_pool[l].normal_(generator=g)
+            self.v_pool[l].normal_(generator=g)
+        self.q = torch.randn(LAYERS, BATCH, Q_HEADS * HEAD, generator=g, dtype=torch.float16, device=device)
+        self.k = torch.randn(LAYERS, BATCH, KV_HEADS * HEAD, generator=g, dtype=torch.float16, device=device)
+        self.v = torch.randn(LAYERS, BATCH, KV_HEADS * HEAD, generator=g, dtype=torch.float16, device=device)
+        self.out = torch.empty_like(self.q)
+        max_pos = int(final.max()) + 1
+        self.sin = torch.empty(max_pos, HEAD, dtype=torch.float32, device=device)
+        self.cos = torch.empty(max_pos, HEAD, dtype=torch.float32, device=device)
+        capi.sin_cos_cache(self.sin, self.cos, HEAD, max_pos, ROPE_THETA)
+        self.ws_bytes = capi.decode_workspace_bytes(BATCH, Q_HEADS, KV_HEADS, HEAD)
+        self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=device)
+        capi.workspace_init(self.ws, self.ws_bytes)
+        self.scale = 1.0 / float(np.sqrt(HEAD))
+        self.launches = 0
+        # host side of the end-to-end path
+        self.h_q = self.q.cpu().pin_memory()
+        self.h_k = self.k.cpu().pin_memory()
+        self.h_v = self.v.cpu().pin_memory()
+        self.h_out = torch.empty_like(self.h_q).pin_memory()
+        self._prepare_pointers()
+        torch.cuda.synchronize(device)
+
+    def _prepare_pointers(self):
+        """Raw device addresses, so the per-layer host work is two C calls and nothing else."""
+        self.p_kpool = [self.k_pool[l].data_ptr() for l in range(LAYERS)]
+        self.p_vpool = [self.v_pool[l].data_ptr() for l in range(LAYERS)]
+        self.p_q = [self.q[l].data_ptr() for l in range(LAYERS)]
+        self.p_k = [self.k[l].data_ptr() for l in range(LAYERS)]
+        self.p_v = [self.v[l].data_ptr() for l in range(LAYERS)]
+        self.p_out = [self.out[l].data_ptr() for l in range(LAYERS)]
+        self.p_pos, self.p_slots = self.positions.data_ptr(), self.slots.data_ptr()
+        self.p_sin, self.p_cos = self.sin.data_ptr(), self.cos.data_ptr()
+        self.p_table, self.p_ws = self.table.data_ptr(), self.ws.data_ptr()
+        self.stream = self.torch.cuda.current_stream().cuda_stream
+
+    def layer(self, t, l, events=None):
+        capi = self.capi
+        pos = self.p_pos + t * BATCH * 4
+        capi.rope_append(self.p_q[l], self.p_k[l], self.p_v[l], Q_HEADS, pos, self.p_sin, self.p_cos,
+                         self.p_kpool[l], self.p_vpool[l], self.layout, self.p_slots + t * BATCH * 8,
+                         BATCH, stream=self.stream)
+        if events is not None:
+            events[0].record()
+        # tokens cached before the step + 1 appended = attended length (len_bias = 1)
+        capi.paged_decode(self.p_out[l], self.p_q[l], self.p_kpool[l], self.p_vpool[l], self.layout,
+                          self.p_table, self.max_blocks, pos, 1, BATCH, Q_HEADS, self.scale,
+                          self.p_ws, self.ws_bytes, stream=self.stream)
+        if events is not None:
+            events[1].record()
+        self.launches += 2
+
+    def step_resident(self, t, event_sink=None):
+        for l in range(LAYERS):
+            ev = None
+            if event_sink is not None:
+                ev = (self.torch.cuda.Event(enable_timing=True), self.torch.cuda.Event(enable_timing=True))
+                event_sink.append(ev)
+            self.layer(t, l, ev)
+
+    def step_e2e(self, t):
+        # Q/K/V rows of the step come from pinned host memory, outputs return to it
+        for l in range(LAYERS):
+            self.q[l].copy_(self.h_q[l], non_blocking=True)
+            self.k[l].copy_(self.h_k[l], non_blocking=True)
+            self.v[l].copy_(self.h_v[l], non_blocking=True)
+            self.layer(t, l)
+            self.h_out[l].copy_(self.out[l], non_blocking=True)
+
+    def kv_bytes_step(self, t):
+        return kv_bytes_per_layer(self.lens0 + t + 1) * LAYERS
+
+    def h2d_bytes_per_step(self):
+        return LAYERS * BATCH * (Q_HEADS + 2 * KV_HEADS) * HEAD * 2
+
+    def d2h_bytes_per_step(self):
+        return LAYERS * BATCH * Q_HEADS * HEAD * 2
+
+
+# ------------------------------------------------------------------ CPU legs (oracle)
+def cpu_decode_sample(threads, reps, seed=SEED):
+    """Times the CPU restatement of the reference's fp32 MHA path (the oracle: test
+    infrastructure, used here only as the reported baseline) on ONE layer of the workload:
+    all 64 sequences, fp32 pools gathered through the block table.  Returns GB/s in the same
+    algorithmic bytes as the GPU arm (fp16 K+V rows of every cached token)."""
+    from tests import kvtest
+    orc = kvtest.load_oracle()
+    lens = make_lens(seed) + 1
+    rng = np.random.default_rng(seed + 7)
+    nblk = (lens + BLOCK - 1) // BLOCK
+    num_blocks = int(np.ceil(int(nblk.sum()) * 1.25))
+    perm = rng.permutation(num_blocks).astype(np.int32)
+    table = np.zeros((BATCH, int(nblk.max())), np.int32)
+    c = 0
+    for i, n in enumerate(nblk):
+        table[i, :n] = perm[c:c + n]
+        c += n
+    kp = rng.standard_normal((num_blocks, KV_HEADS, BLOCK, HEAD), np.float32)
+    vp = rng.standard_normal((num_blocks, KV_HEADS, BLOCK, HEAD), np.float32)
+    q = rng.standard_normal((BATCH, Q_HEADS * HEAD), np.float32)
+    orc.paged_decode(q[:2], kp, vp, table[:2], lens[:2], Q_HEADS, KV_HEADS, HEAD, BLOCK, threads)  # warm
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        orc.paged_decode(q, kp, vp, table, lens, Q_HEADS, KV_HEADS, HEAD, BLOCK, threads)
+        times.append(time.perf_counter() - t0)
+    nbytes = kv_bytes_per_layer(lens)
+    return nbytes / 1e9 / float(np.mean(times)), float(np.mean(times)), nbytes
+
+
+def run_reference(args):
+    """Reference arm: the reference's own CPU path for this hot path cannot be compiled here
+    (it needs Armadillo + glog), so the timed code is its restatement under oracle/, on all
+    host threads.  One step = one layer of the workload (a bounded sample of the 36)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from tests import kvtest
+    threads = kvtest.load_oracle().max_threads()
+    reps = args.warmup + args.steps
+    gbs, sec, nbytes = cpu_decode_sample(threads, max(1, args.steps))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "paged GQA decode, Qwen3-8B attention shape, bs=64, ctx U[128,4096], block 16",
+                   "sample": "1 of 36 layers per step, all 64 sequences"},
+        "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": "one layer (all 64 sequences, %d KV bytes) per step, fp32 oracle" % nbytes},
+        "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "tokens_per_s": round(BATCH / (sec * LAYERS), 3),
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    from orinmllm_b200 import build
+    if not (build.LIB / "libkpx.so").exists():
+        build.build_all()
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    W, K = args.warmup, args.steps
+    total_steps = 2 * (W + K)
+    wl = DecodeWorkload(rank, total_steps, device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    # ---- device-resident phase ----
+    t = 0
+    for _ in range(W):
+        wl.step_resident(t)
+        t += 1
+    barrier()
+    if sampler:
+        sampler.start()
+    wl.launches = 0
+    pairs = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    bytes_resident = 0
+    e0.record()
+    for _ in range(K):
+        wl.step_resident(t, pairs)
+        bytes_resident += wl.kv_bytes_step(t)
+        t += 1
+    e1.record()
+    barrier()
+    ms_resident = max_over_ranks(e0.elapsed_time(e1))
+    launches = wl.launches
+    decode_ms = [a.elapsed_time(b) for a, b in pairs]
+    # ---- end-to-end phase (host buffers) ----
+    for _ in range(W):
+        wl.step_e2e(t)
+        t += 1
+    barrier()
+    bytes_e2e = 0
+    e0.record()
+    for _ in range(K):
+        wl.step_e2e(t)
+        bytes_e2e += wl.kv_bytes_step(t)
+        t += 1
+    e1.record()
+    barrier()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1))
+    clocks = sampler.stop() if sampler else None
+    status = wl.capi.workspace_status(wl.ws)
+    if status != 0:
+        raise SystemExit(f"device status {status}: {wl.capi.status_string(status)}")
+    # whole-job totals (every rank holds the same amount of work: weak scaling)
+    tot = torch.tensor([bytes_resident, bytes_e2e], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(tot)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peak, peak_src = peaks()
+    value = tot[0].item() / 1e9 / (ms_resident / 1e3)
+    e2e = tot[1].item() / 1e9 / (ms_e2e / 1e3)
+    per_launch_bytes = bytes_resident / (K * LAYERS)
+    avg_decode_ms = float(np.mean(decode_ms))
+    achieved = per_launch_bytes / 1e9 / (avg_decode_ms / 1e3)
+    cpu_gbs, cpu_sec, cpu_bytes = cpu_decode_sample(1, 3)
+    line = {
+        "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": K,
+        "warmup": W, "ms_per_step": round(ms_resident / K, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage, f32 arithmetic", "data": "synthetic",
+        "config": {"workload": "paged GQA decode, Qwen3-8B attention shape (32 Q / 8 KV heads, d=128), "
+                               "fp16 KV, block 16, bs=64 per GPU, ctx U[128,4096], pool x1.25, "
+                               "seeded random block table; step = RoPE+append+attend over 36 layers",
+                   "layers": LAYERS, "batch_per_gpu": BATCH, "partition": "by request, no collective",
+                   "l2": "inputs larger than L2: every layer has its own 0.66 GB pool"},
+        "tokens_per_s": round(world * BATCH / (ms_resident / K / 1e3), 1),
+        "pct_of_8TBs_per_gpu": round(100 * value / world / 8000.0, 2),
+        "e2e": {"value": round(e2e, 1), "unit": "GB/s", "h2d_bytes_per_step": wl.h2d_bytes_per_step(),
+                "d2h_bytes_per_step": wl.d2h_bytes_per_step(), "ms_per_step": round(ms_e2e / K, 4),
+                "tokens_per_s": round(world * BATCH / (ms_e2e / K / 1e3), 1)},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "kernel": "paged_decode_kernel", "achieved": round(achieved, 1),
+                     "peak": peak, "peak_source": peak_src, "unit": "GB/s",
+                     "frac": round(achieved / peak, 4), "avg_launch_us": round(avg_decode_ms * 1e3, 2),
+                     "algorithmic_bytes_per_launch": int(per_launch_bytes),
+                     "traffic": int(per_launch_bytes * TRAFFIC_RATIO), "traffic_note": TRAFFIC_NOTE},
+        "cpu_baseline": {"value": round(cpu_gbs, 3), "unit": "GB/s", "cores": 1, "kind": "port",
+                         "sample": "one layer of the workload (64 sequences, %d KV bytes), fp32 oracle, "
+                                   "mean of 3 runs, %.2f s each" % (cpu_bytes, cpu_sec)},
+        "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram bytes (read+write) / algorithmic bytes of one decode launch, from the ncu capture
+# summarised in profiles/ (same kernel, same shape, one layer)
+TRAFFIC_RATIO = 1.019
+TRAFFIC_NOTE = "ncu dram__bytes_read+write of one launch at this shape / algorithmic bytes = 1.019"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()
