@@ -32,7 +32,8 @@ enum {
   KPX_ERR_WORKSPACE_TOO_SMALL = 10,
   KPX_ERR_DEVICE_TIMEOUT = 11,
   KPX_ERR_REFCOUNT = 12,
-  KPX_ERR_NOT_FOUND = 13
+  KPX_ERR_NOT_FOUND = 13,
+  KPX_ERR_STATIC_SCRATCH_LIMIT = 14
 };
 
 /* Element types of pools, queries and outputs (base::DataType has Fp32 and Fp16,
@@ -130,6 +131,27 @@ KPX_API int kpx_paged_decode(void* out, const void* q, const void* k_pool, const
                              int32_t max_blocks_per_seq, const int32_t* seq_lens,
                              int32_t len_bias, int32_t batch, int32_t num_q_heads, float scale,
                              void* workspace, int64_t workspace_bytes, void* stream);
+
+/* kpx_paged_decode for callers that cannot allocate or pass scratch memory: a plugin
+ * inside a host that owns the device heap, a kernel registry whose signature carries only
+ * inputs and outputs (the reference's MHAKernel is one), code that may not call cudaMalloc
+ * between steps.  Same arguments and results as kpx_paged_decode minus the workspace; the
+ * scratch is a 10 715 392-byte array built into the library, which every GPU that loads
+ * the library holds until the process exits.  It allocates nothing (no cudaMalloc /
+ * cudaFree / allocating library call).
+ * Limits: num_kv_heads * ceil(kv_mul / 4) <= 16 (kv_mul = num_q_heads / num_kv_heads; for
+ * kv_mul 1 or 2 the factor is 1); anything larger returns KPX_ERR_STATIC_SCRATCH_LIMIT.
+ * The first call on each device looks up the array's device address (and sets kernel
+ * attributes); make that first call before any stream capture.  All calls on a device
+ * share the one array: calls that overlap on the GPU (different streams) race and must be
+ * serialised by the caller; calls on one stream are fine.  The status word is cleared at
+ * the start of every call and is not readable through this entry point.
+ * This entry point has no counterpart in the reference. */
+KPX_API int kpx_paged_decode_static(void* out, const void* q, const void* k_pool,
+                                    const void* v_pool, const kpx_kv_layout* layout,
+                                    const int32_t* block_table, int32_t max_blocks_per_seq,
+                                    const int32_t* seq_lens, int32_t len_bias, int32_t batch,
+                                    int32_t num_q_heads, float scale, void* stream);
 
 /* A workspace starts with a 256-byte header whose first word is a sticky status
  * the kernels raise (never clear).  kpx_workspace_init zeroes the header (async on

@@ -23,6 +23,7 @@ KPX_ERR_WORKSPACE_TOO_SMALL = 10
 KPX_ERR_DEVICE_TIMEOUT = 11
 KPX_ERR_REFCOUNT = 12
 KPX_ERR_NOT_FOUND = 13
+KPX_ERR_STATIC_SCRATCH_LIMIT = 14
 
 
 class KvLayout(C.Structure):
@@ -55,6 +56,7 @@ SIGNATURES = {
     "kpx_decode_workspace_bytes": (_I64, [_I32, _I32, _I32, _I32]),
     "kpx_paged_decode": (C.c_int, [_P, _P, _P, _P, _LP, _P, _I32, _P, _I32, _I32, _I32, _F32,
                                    _P, _I64, _P]),
+    "kpx_paged_decode_static": (C.c_int, [_P, _P, _P, _P, _LP, _P, _I32, _P, _I32, _I32, _I32, _F32, _P]),
     "kpx_workspace_init": (C.c_int, [_P, _I64, _P]),
     "kpx_workspace_status": (C.c_int, [_P, _P]),
     "kpx_prefill_workspace_bytes": (_I64, [_I32, _I32, _I32, _I32]),
@@ -182,6 +184,15 @@ def paged_decode(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq
                                  ptr(block_table), max_blocks_per_seq, ptr(seq_lens), len_bias,
                                  batch, num_q_heads, scale, ptr(workspace), workspace_bytes,
                                  _stream(stream)), "kpx_paged_decode")
+
+
+def paged_decode_static(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq, seq_lens,
+                        len_bias, batch, num_q_heads, scale, stream=None) -> None:
+    """Decode with the library's built-in scratch array (no workspace argument, no allocation)."""
+    check(lib().kpx_paged_decode_static(ptr(out), ptr(q), ptr(k_pool), ptr(v_pool), C.byref(layout),
+                                        ptr(block_table), max_blocks_per_seq, ptr(seq_lens),
+                                        len_bias, batch, num_q_heads, scale, _stream(stream)),
+          "kpx_paged_decode_static")
 
 
 def prefill_workspace_bytes(total_q, num_q_heads, num_kv_heads, head_size=128) -> int:

@@ -47,6 +47,8 @@ extern "C" const char* kpx_status_string(int status) {
     case KPX_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
     case KPX_ERR_REFCOUNT: return "block reference count would become negative";
     case KPX_ERR_NOT_FOUND: return "not found";
+    case KPX_ERR_STATIC_SCRATCH_LIMIT:
+      return "beyond the limits of the built-in scratch array (num_kv_heads * head groups > 16)";
     default: return "unknown status";
   }
 }

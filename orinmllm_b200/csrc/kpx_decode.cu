@@ -20,6 +20,7 @@
 // math is fp32 on CUDA cores (packed fp32x2 FMAs); softmax is online with warp
 // shuffles.  Every mbarrier wait is bounded; a wait that gives up raises the
 // workspace status word and the warp retires.
+#include <mutex>
 #include <type_traits>
 
 #include "kpx_common.cuh"
@@ -748,4 +749,70 @@ extern "C" int kpx_paged_decode(void* out, const void* q, const void* k_pool, co
     if (rc != KPX_OK) return rc;
   }
   return KPX_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Decode without a caller-provided workspace.
+//
+// Some callers cannot hand over scratch memory: a plugin running inside a host that owns
+// the whole device heap, code on a stream whose owner forbids cudaMalloc between steps, a
+// kernel registry that only passes inputs and outputs.  For them the scratch of
+// kpx_paged_decode (status word, per-item piece counters, split-KV partials) lives in the
+// array below: file-scope device memory that every GPU loading this library holds until
+// the process exits.
+namespace kpx {
+namespace {
+constexpr int kStaticMaxItemsPerSeq = 16;  // num_kv_heads * head groups, e.g. 8 KV heads x 8 query heads each
+constexpr int64_t kStaticCounterBytes = int64_t(kMaxBatch) * kStaticMaxItemsPerSeq * 4;
+constexpr int64_t kStaticScratchBytes =
+    kStatusBytes + kStaticCounterBytes +
+    int64_t(2) * kMaxSms * kMaxWarpsPerCta * (4 * kD + 8) * sizeof(float);  // 10 715 392 bytes
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+}  // namespace
+}  // namespace kpx
+
+extern "C" int kpx_paged_decode_static(void* out, const void* q, const void* k_pool,
+                                       const void* v_pool, const kpx_kv_layout* layout,
+                                       const int32_t* block_table, int32_t max_blocks_per_seq,
+                                       const int32_t* seq_lens, int32_t len_bias, int32_t batch,
+                                       int32_t num_q_heads, float scale, void* stream) {
+  if (!layout_ok(layout) || num_q_heads <= 0 || num_q_heads % layout->num_kv_heads)
+    return KPX_ERR_INVALID_ARGUMENT;
+  const int kv_mul = num_q_heads / layout->num_kv_heads;
+  const int qh = heads_per_warp(kv_mul);
+  const int per_seq = layout->num_kv_heads * ((kv_mul + qh - 1) / qh);
+  if (per_seq > kStaticMaxItemsPerSeq) return KPX_ERR_STATIC_SCRATCH_LIMIT;
+  const int64_t need =
+      kpx_decode_workspace_bytes(batch, num_q_heads, layout->num_kv_heads, layout->head_size);
+  if (need < 0) return KPX_ERR_UNIMPLEMENTED;
+  if (need > kStaticScratchBytes) return KPX_ERR_STATIC_SCRATCH_LIMIT;
+  if (!device_info().ok) return KPX_ERR_CUDA;
+  // In host code `g_static_scratch` names a host-side stand-in, not device memory: the
+  // address a kernel may use comes from cudaGetSymbolAddress, asked once per device with
+  // that device current.
+  static void* scratch_of_device[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  KPX_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return KPX_ERR_CUDA;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!scratch_of_device[dev]) {
+      void* ptr = nullptr;
+      if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) {
+        (void)cudaGetLastError();
+        return KPX_ERR_CUDA;
+      }
+      scratch_of_device[dev] = ptr;
+    }
+    scratch = scratch_of_device[dev];
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left: the status word and the piece
+  // counters must start at zero (partials are always written before they are read).
+  KPX_CUDA_TRY(cudaMemsetAsync(scratch, 0, size_t(kStatusBytes + kStaticCounterBytes), s));
+  return kpx_paged_decode(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq,
+                          seq_lens, len_bias, batch, num_q_heads, scale, scratch,
+                          kStaticScratchBytes, stream);
 }
