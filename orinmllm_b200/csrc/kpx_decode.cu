@@ -40,6 +40,7 @@ struct DecodeParams {
   const uint8_t* v_pool;
   const int32_t* block_table;
   const int32_t* seq_lens;
+  const int32_t* row_index;  // table row of each batch entry (nullptr: entry b uses row b)
   float* partials;
   int32_t* counters;  // one per item, zero between launches
   int32_t* status;
@@ -82,7 +83,9 @@ struct Cursor {
   const int32_t* row;  // block-table row of sequence b (nullptr: identity table)
   __device__ __forceinline__ void refresh(const DecodeParams& p) {
     kvh = sub / p.head_groups;
-    row = p.block_table ? p.block_table + int64_t(b) * p.max_blocks_per_seq : nullptr;
+    row = p.block_table
+              ? p.block_table + int64_t(p.row_index ? p.row_index[b] : b) * p.max_blocks_per_seq
+              : nullptr;
   }
   __device__ __forceinline__ void locate(const DecodeParams& p, const int* prefix, int64_t u) {
     const int per_seq = p.num_kv_heads * p.head_groups;
@@ -695,6 +698,16 @@ extern "C" int kpx_paged_decode(void* out, const void* q, const void* k_pool, co
                                 int32_t max_blocks_per_seq, const int32_t* seq_lens,
                                 int32_t len_bias, int32_t batch, int32_t num_q_heads, float scale,
                                 void* workspace, int64_t workspace_bytes, void* stream) {
+  return kpx::decode_rows(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq, nullptr,
+                          seq_lens, len_bias, batch, num_q_heads, scale, workspace, workspace_bytes,
+                          stream);
+}
+
+int kpx::decode_rows(void* out, const void* q, const void* k_pool, const void* v_pool,
+                     const kpx_kv_layout* layout, const int32_t* block_table,
+                     int32_t max_blocks_per_seq, const int32_t* row_index, const int32_t* seq_lens,
+                     int32_t len_bias, int32_t batch, int32_t num_q_heads, float scale,
+                     void* workspace, int64_t workspace_bytes, void* stream) {
   if (!layout_ok(layout) || !out || !q || !k_pool || !v_pool || batch < 0 || num_q_heads <= 0)
     return KPX_ERR_INVALID_ARGUMENT;
   if (layout->head_size != kD || layout->block_size != kBS) return KPX_ERR_UNIMPLEMENTED;
@@ -738,7 +751,9 @@ extern "C" int kpx_paged_decode(void* out, const void* q, const void* k_pool, co
     p.batch = nb;
     p.out = static_cast<uint8_t*>(out) + int64_t(b0) * num_q_heads * kD * eb;
     p.q = static_cast<const uint8_t*>(q) + int64_t(b0) * num_q_heads * kD * eb;
-    p.block_table = block_table ? block_table + int64_t(b0) * max_blocks_per_seq : nullptr;
+    p.row_index = row_index ? row_index + b0 : nullptr;
+    p.block_table = (block_table && !row_index) ? block_table + int64_t(b0) * max_blocks_per_seq
+                                                : block_table;
     p.seq_lens = seq_lens ? seq_lens + b0 : nullptr;
     int rc;
     switch (layout->dtype) {
