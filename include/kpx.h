@@ -88,14 +88,16 @@ KPX_API int kpx_append(void* k_pool, void* v_pool, const kpx_kv_layout* layout, 
  * on num_tokens rows of Q [num_tokens, q_heads*head_size] and K, in place, with
  * sin/cos read from fp32 tables [max_pos, head_size] at index pos*head_size + 2j;
  * then, if k_pool is not NULL, the rotated K rows and the V rows are appended as
- * kpx_append does.  positions is a device int32 array [num_tokens].  The products
+ * kpx_append does.  Token t sits at position positions[t] + pos_base (positions: device
+ * int32 [num_tokens]) or, with positions NULL, at pos_base + t (a chunk starting at
+ * pos_base, the reference's batched RoPE).  The products
  * are not contracted into FMAs, so the result is bit-identical to the reference
  * CPU statement when both read the same tables.
  * Replaces rope_kernel_cu / _gpu_pos / _fp16_gpu_pos / batched_rope_kernel_cu
  * (kuiper/source/op/kernels/cuda/rope_kernel.cuh:5-28), CPU statement
  * kuiper/source/op/kernels/cpu/rope_kernel.cpp:58-82.  q or k may be NULL. */
 KPX_API int kpx_rope_append(void* q, void* k, const void* v, int32_t q_heads,
-                            const int32_t* positions, const float* sin_cache,
+                            const int32_t* positions, int32_t pos_base, const float* sin_cache,
                             const float* cos_cache, void* k_pool, void* v_pool,
                             const kpx_kv_layout* layout, const int64_t* slot_mapping,
                             int32_t num_tokens, void* stream);

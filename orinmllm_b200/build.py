@@ -125,6 +125,21 @@ def build_oracle(verbose=False) -> Path:
     return odir / "liborinkv_oracle.so"
 
 
+def build_cpp_tests(force=False, verbose=False) -> Path:
+    """Compile tests/cpp/test_kuiper_api.cu (layer API vs the CPU oracle; test infrastructure,
+    the only binary that links the oracle) into lib/test_kuiper_api."""
+    src = ROOT / "tests" / "cpp" / "test_kuiper_api.cu"
+    exe = LIB / "test_kuiper_api"
+    oracle_so = build_oracle(verbose)
+    if force or _newer(exe, [src, LIB / "libkpx.so", oracle_so] + _headers()):
+        _run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17",
+              "-I", INCLUDE, "-I", INCLUDE / "kuiper", "-o", exe, src, f"-L{LIB}", "-lkpx",
+              f"-L{ROOT / 'oracle'}", "-lorinkv_oracle",
+              "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN",
+              "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../oracle"], verbose)
+    return exe
+
+
 def build_all(force=False, verbose=False, ptxas_info=False):
     build_kpx(force, verbose, ptxas_info)
     build_host(force, verbose)

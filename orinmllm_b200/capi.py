@@ -51,7 +51,7 @@ SIGNATURES = {
     "kpx_layout_paged": (C.c_int, [_LP, _I32, _I32, _I32, _I32]),
     "kpx_layout_contiguous": (C.c_int, [_LP, _I32, _I32, _I32, _I32]),
     "kpx_append": (C.c_int, [_P, _P, _LP, _P, _P, _P, _P, _I32, _I32, _P]),
-    "kpx_rope_append": (C.c_int, [_P, _P, _P, _I32, _P, _P, _P, _P, _P, _LP, _P, _I32, _P]),
+    "kpx_rope_append": (C.c_int, [_P, _P, _P, _I32, _P, _I32, _P, _P, _P, _P, _LP, _P, _I32, _P]),
     "kpx_sin_cos_cache": (C.c_int, [_P, _P, _I32, _I32, _F32, _P]),
     "kpx_decode_workspace_bytes": (_I64, [_I32, _I32, _I32, _I32]),
     "kpx_paged_decode": (C.c_int, [_P, _P, _P, _P, _LP, _P, _I32, _P, _I32, _I32, _I32, _F32,
@@ -151,8 +151,8 @@ def append(k_pool, v_pool, layout, k_src, v_src, slot_mapping=None, pos_dev=None
 
 
 def rope_append(q, k, v, q_heads, positions, sin_cache, cos_cache, k_pool, v_pool, layout,
-                slot_mapping, num_tokens, stream=None) -> None:
-    check(lib().kpx_rope_append(ptr(q), ptr(k), ptr(v), q_heads, ptr(positions), ptr(sin_cache),
+                slot_mapping, num_tokens, stream=None, pos_base=0) -> None:
+    check(lib().kpx_rope_append(ptr(q), ptr(k), ptr(v), q_heads, ptr(positions), pos_base, ptr(sin_cache),
                                 ptr(cos_cache), ptr(k_pool), ptr(v_pool), C.byref(layout),
                                 ptr(slot_mapping), num_tokens, _stream(stream)), "kpx_rope_append")
 

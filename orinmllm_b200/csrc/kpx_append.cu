@@ -65,7 +65,7 @@ __global__ void append_kernel(uint8_t* __restrict__ k_pool, uint8_t* __restrict_
 template <typename T>
 __global__ void rope_append_kernel(T* __restrict__ q, T* __restrict__ k, const T* __restrict__ v,
                                    int32_t q_heads, const int32_t* __restrict__ positions,
-                                   const float* __restrict__ sin_cache,
+                                   int32_t pos_base, const float* __restrict__ sin_cache,
                                    const float* __restrict__ cos_cache, uint8_t* __restrict__ k_pool,
                                    uint8_t* __restrict__ v_pool,
                                    const int64_t* __restrict__ slot_mapping, int32_t num_tokens,
@@ -98,7 +98,7 @@ __global__ void rope_append_kernel(T* __restrict__ q, T* __restrict__ k, const T
     bool is_k = q ? head >= q_heads : true;
     int h = is_k ? head - (q ? q_heads : 0) : head;
     T* row = is_k ? k + (t * kvh + h) * int64_t(hs) : q + (t * q_heads + h) * int64_t(hs);
-    const int32_t pos = positions[t];
+    const int32_t pos = (positions ? positions[t] : int32_t(t)) + pos_base;
     uint4 lo_raw = *reinterpret_cast<const uint4*>(row + g * E);
     uint4 hi_raw = *reinterpret_cast<const uint4*>(row + hs / 2 + g * E);
     float lo[E], hi[E];
@@ -240,7 +240,7 @@ extern "C" int kpx_append(void* k_pool, void* v_pool, const kpx_kv_layout* layou
 
 template <typename T>
 static int launch_rope(void* q, void* k, const void* v, int32_t q_heads, const int32_t* positions,
-                       const float* sin_cache, const float* cos_cache, void* k_pool, void* v_pool,
+                       int32_t pos_base, const float* sin_cache, const float* cos_cache, void* k_pool, void* v_pool,
                        const LayoutDev& L, const int64_t* slot_mapping, int32_t num_tokens,
                        cudaStream_t stream) {
   constexpr int E = Elt<T>::kPer16B;
@@ -251,18 +251,18 @@ static int launch_rope(void* q, void* k, const void* v, int32_t q_heads, const i
   if (work == 0) return KPX_OK;
   const int threads = 256;
   rope_append_kernel<T><<<grid_for(work, threads), threads, 0, stream>>>(
-      static_cast<T*>(q), static_cast<T*>(k), static_cast<const T*>(v), q_heads, positions,
+      static_cast<T*>(q), static_cast<T*>(k), static_cast<const T*>(v), q_heads, positions, pos_base,
       sin_cache, cos_cache, static_cast<uint8_t*>(k_pool), static_cast<uint8_t*>(v_pool),
       slot_mapping, num_tokens, L);
   return cuda_status(cudaGetLastError());
 }
 
 extern "C" int kpx_rope_append(void* q, void* k, const void* v, int32_t q_heads,
-                               const int32_t* positions, const float* sin_cache,
+                               const int32_t* positions, int32_t pos_base, const float* sin_cache,
                                const float* cos_cache, void* k_pool, void* v_pool,
                                const kpx_kv_layout* layout, const int64_t* slot_mapping,
                                int32_t num_tokens, void* stream) {
-  if (!layout_ok(layout) || !positions || !sin_cache || !cos_cache || num_tokens < 0)
+  if (!layout_ok(layout) || !sin_cache || !cos_cache || num_tokens < 0)
     return KPX_ERR_INVALID_ARGUMENT;
   if (q && q_heads <= 0) return KPX_ERR_INVALID_ARGUMENT;
   if (k_pool && !slot_mapping) return KPX_ERR_INVALID_ARGUMENT;
@@ -276,11 +276,11 @@ extern "C" int kpx_rope_append(void* q, void* k, const void* v, int32_t q_heads,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (layout->dtype) {
     case KPX_F16:
-      return launch_rope<__half>(q, k, v, q_heads, positions, sin_cache, cos_cache, k_pool, v_pool, L, slot_mapping, num_tokens, s);
+      return launch_rope<__half>(q, k, v, q_heads, positions, pos_base, sin_cache, cos_cache, k_pool, v_pool, L, slot_mapping, num_tokens, s);
     case KPX_BF16:
-      return launch_rope<__nv_bfloat16>(q, k, v, q_heads, positions, sin_cache, cos_cache, k_pool, v_pool, L, slot_mapping, num_tokens, s);
+      return launch_rope<__nv_bfloat16>(q, k, v, q_heads, positions, pos_base, sin_cache, cos_cache, k_pool, v_pool, L, slot_mapping, num_tokens, s);
     default:
-      return launch_rope<float>(q, k, v, q_heads, positions, sin_cache, cos_cache, k_pool, v_pool, L, slot_mapping, num_tokens, s);
+      return launch_rope<float>(q, k, v, q_heads, positions, pos_base, sin_cache, cos_cache, k_pool, v_pool, L, slot_mapping, num_tokens, s);
   }
 }
 

@@ -42,3 +42,14 @@ def test_argument_validation_without_gpu(native_libs):
     assert L.kpx_paged_decode(None, None, None, None, ctypes.byref(lay), None, 0, None, 0, 1, 32, 1.0, None, 0, None) == capi.KPX_ERR_INVALID_ARGUMENT
     assert capi.decode_workspace_bytes(64, 32, 8, 128) > 0
     assert L.kpx_decode_workspace_bytes(64, 32, 8, 96) < 0
+
+
+def test_host_manager_library_exports_every_declared_symbol(native_libs):
+    from orinmllm_b200 import build, kvm
+    so = build.build_host()
+    text = (ROOT / "include" / "kpx_kvm.h").read_text()
+    declared = sorted(set(re.findall(r"KPX_API\s+[\w\s\*]+?\b(kpx_kvm_\w+)\s*\(", text)))
+    assert len(declared) >= 20
+    handle = ctypes.CDLL(str(so))
+    assert not [s for s in declared if not hasattr(handle, s)]
+    assert sorted(kvm.SIGNATURES) == declared
