@@ -6,10 +6,19 @@
 //     reference's one-CTA-per-query prefill kernels, on the split-KV decode kernel).  Exact
 //     for every dtype and size; K/V traffic grows with queries x keys.
 //   * tensor-core tiles (16-bit caches): see kpx_prefill_tc.cu.
+#include <vector>
+
 #include "kpx_common.cuh"
 
 namespace kpx {
+int prefill_tc(void* out, const void* q, const void* k_pool, const void* v_pool, const kpx_kv_layout* layout,
+               const int32_t* block_table, int32_t max_blocks_per_seq, const int32_t* cu_q_lens_host,
+               const int32_t* start_pos_host, int32_t batch, int32_t num_q_heads, float scale, void* tile_area,
+               int64_t tile_area_bytes, int32_t* status, cudaStream_t stream);
 namespace {
+
+// 0 = tensor-core tiles where the layout allows, else per-query streaming; 1 = always streaming
+int g_prefill_path = 0;
 
 constexpr int kHeaderBytes = 256;
 
@@ -35,13 +44,18 @@ inline int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
 
 using namespace kpx;
 
+extern "C" __attribute__((visibility("default"))) void kpx_internal_set_prefill_path(int v) {
+  g_prefill_path = v;
+}
+
 extern "C" int64_t kpx_prefill_workspace_bytes(int32_t total_q, int32_t num_q_heads,
                                                int32_t num_kv_heads, int32_t head_size) {
   if (total_q < 0) return -1;
   int64_t dec = kpx_decode_workspace_bytes(total_q, num_q_heads, num_kv_heads, head_size);
   if (dec < 0) return -1;
   // decode workspace, then lens[total_q], rows[total_q], cu[<=total_q+1], start[<=total_q]
-  return dec + align256(int64_t(total_q) * 4) * 2 + align256((int64_t(total_q) + 1) * 4) * 2;
+  return dec + align256(int64_t(total_q) * 4) * 2 + align256((int64_t(total_q) + 1) * 4) * 2 +
+         align256((int64_t(total_q) + 1) * 16);  // + tile list of the tensor-core path
 }
 
 extern "C" int kpx_paged_prefill(void* out, const void* q, const void* k_pool, const void* v_pool,
@@ -74,6 +88,13 @@ extern "C" int kpx_paged_prefill(void* out, const void* q, const void* k_pool, c
   int32_t* cu = reinterpret_cast<int32_t*>(base + 2 * align256(int64_t(total_q) * 4));
   int32_t* start = reinterpret_cast<int32_t*>(base + 2 * align256(int64_t(total_q) * 4) +
                                               align256((int64_t(total_q) + 1) * 4));
+  if (g_prefill_path == 0) {
+    uint8_t* tile_area = base + 2 * align256(int64_t(total_q) * 4) + 2 * align256((int64_t(total_q) + 1) * 4);
+    int rc = prefill_tc(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq, cu_q_lens_host,
+                        start_pos_host, batch, num_q_heads, scale, tile_area,
+                        align256((int64_t(total_q) + 1) * 16), static_cast<int32_t*>(workspace), s);
+    if (rc != KPX_ERR_UNIMPLEMENTED) return rc;
+  }
   KPX_CUDA_TRY(cudaMemcpyAsync(cu, cu_q_lens_host, size_t(batch + 1) * 4, cudaMemcpyHostToDevice, s));
   KPX_CUDA_TRY(cudaMemcpyAsync(start, start_pos_host, size_t(batch) * 4, cudaMemcpyHostToDevice, s));
   expand_queries_kernel<<<(total_q + 255) / 256, 256, 0, s>>>(cu, start, batch, total_q, lens, rows);
