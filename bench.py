@@ -240,9 +240,9 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from tests import kvtest
-    threads = kvtest.load_oracle().max_threads()
-    reps = args.warmup + args.steps
+    # all host cores this process may run on (torchrun presets OMP_NUM_THREADS=1, so the OpenMP
+    # default would be a single thread)
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     gbs, sec, nbytes = cpu_decode_sample(threads, max(1, args.steps))
     line = {
         "impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": "GB/s",
@@ -285,12 +285,10 @@ def run_gpu(args):
             dist.barrier()
         torch.cuda.synchronize(device)
 
+    from orinmllm_b200 import multigpu
+
     def max_over_ranks(ms):
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return multigpu.max_over_ranks(ms, world, device)
 
     sampler = ClockSampler(local) if rank == 0 else None
     # ---- device-resident phase ----
@@ -334,16 +332,14 @@ def run_gpu(args):
     if status != 0:
         raise SystemExit(f"device status {status}: {wl.capi.status_string(status)}")
     # whole-job totals (every rank holds the same amount of work: weak scaling)
-    tot = torch.tensor([bytes_resident, bytes_e2e], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(tot)
+    tot = multigpu.sum_over_ranks([bytes_resident, bytes_e2e], world, device)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
     peak, peak_src = peaks()
-    value = tot[0].item() / 1e9 / (ms_resident / 1e3)
-    e2e = tot[1].item() / 1e9 / (ms_e2e / 1e3)
+    value = tot[0] / 1e9 / (ms_resident / 1e3)
+    e2e = tot[1] / 1e9 / (ms_e2e / 1e3)
     per_launch_bytes = bytes_resident / (K * LAYERS)
     avg_decode_ms = float(np.mean(decode_ms))
     achieved = per_launch_bytes / 1e9 / (avg_decode_ms / 1e3)
