@@ -53,7 +53,7 @@ struct DecodeParams {
   float qscale;  // softmax scale * log2(e)
 };
 
-template <typename T, int QH, int NW, int NS>
+template <typename T, int QH, int NW, int NS, int LPT>
 struct Cfg {
   static constexpr int kEltB = sizeof(T);
   static constexpr int kTileB = kBS * kD * kEltB;  // one (block, head) tile of K or of V
@@ -119,20 +119,33 @@ struct Cursor {
   }
 };
 
-__device__ __forceinline__ int64_t range_start(int64_t total, int64_t c, int64_t g) {
-  return (total * c) / g;
-}
+// The line of `total` blocks is cut into W contiguous ranges: the first `rem` ranges hold
+// quot+1 blocks, the others quot (quot = total / W, rem = total % W).  Starts and owners need
+// one multiply / one division by a small number instead of 64-bit divisions by W.
+struct Split {
+  int64_t quot, rem;
+  __device__ __forceinline__ int64_t start(int64_t c) const { return c * quot + (c < rem ? c : rem); }
+  __device__ __forceinline__ int64_t owner(int64_t u) const {
+    const int64_t big = rem * (quot + 1);  // blocks held by the ranges of quot+1
+    if (u < big) return (big >> 31) ? u / (quot + 1) : int64_t(uint32_t(u) / uint32_t(quot + 1));
+    const int64_t v = u - big;
+    return rem + ((v >> 31) || (quot >> 31) ? v / quot : int64_t(uint32_t(v) / uint32_t(quot)));
+  }
+};
 
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-template <typename T, int QH, int NW, int NS>
-__global__ void __launch_bounds__(Cfg<T, QH, NW, NS>::kThreads, 1)
+template <typename T, int QH, int NW, int NS, int LPT>
+__global__ void __launch_bounds__(Cfg<T, QH, NW, NS, LPT>::kThreads, 1)
 paged_decode_kernel(const DecodeParams p) {
-  using C = Cfg<T, QH, NW, NS>;
+  using C = Cfg<T, QH, NW, NS, LPT>;
   constexpr int E = Elt<T>::kPer16B;  // elements per 16-byte vector
-  constexpr int NCH = 16 / E;         // 16-byte chunks per thread per row (16 dims per thread)
+  // LPT lanes share one token row: each owns DPT = 128/LPT dims; a warp covers TG = 32/LPT
+  // token rows per pass and R = 16/TG passes per block.
+  constexpr int TG = 32 / LPT, R = kBS / TG, DPT = kD / LPT, HP = DPT / 2;
+  constexpr int NCH = DPT / E;        // 16-byte chunks per thread per row
   constexpr int NV = (QH == 4) ? 2 : 1;  // finished scores per thread per block
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x;
@@ -149,13 +162,6 @@ paged_decode_kernel(const DecodeParams p) {
     mbar_fence_init();
   }
   for (int b = tid; b < p.batch; b += C::kThreads) prefix[b + 1] = blocks_of(seq_len_of(p, b));
-  if (blockIdx.x == 0) {  // a sequence without tokens gets zeros (no warp ever visits it)
-    for (int b = 0; b < p.batch; ++b) {
-      if (seq_len_of(p, b) > 0) continue;
-      T* o = static_cast<T*>(p.out) + int64_t(b) * p.num_q_heads * kD;
-      for (int e = tid; e < p.num_q_heads * kD; e += C::kThreads) o[e] = Elt<T>::from_float(0.f);
-    }
-  }
   if (tid == 0) prefix[0] = 0;
   __syncthreads();
   if (warp == 0) {  // inclusive scan in chunks of 32
@@ -173,18 +179,27 @@ paged_decode_kernel(const DecodeParams p) {
     }
   }
   __syncthreads();
+  // a sequence without tokens gets zeros (no warp ever visits it); CTAs share the rows
+  for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
+    if (prefix[b + 1] != prefix[b]) continue;
+    T* o = static_cast<T*>(p.out) + int64_t(b) * p.num_q_heads * kD;
+    for (int e = tid; e < p.num_q_heads * kD; e += C::kThreads) o[e] = Elt<T>::from_float(0.f);
+  }
   const int64_t total = int64_t(prefix[p.batch]) * p.num_kv_heads * p.head_groups;
   const int64_t W = int64_t(gridDim.x) * C::kWarps;
   const int64_t worker = int64_t(blockIdx.x) * C::kWarps + warp;
-  const int64_t u0 = range_start(total, worker, W), u1 = range_start(total, worker + 1, W);
+  Split split;
+  split.quot = total / W;
+  split.rem = total - split.quot * W;
+  const int64_t u0 = split.start(worker), u1 = split.start(worker + 1);
   if (u0 >= u1) return;  // nothing below synchronises across warps
   const int n = int(u1 - u0);
 
-  const int tg = lane >> 3;  // token group: tokens it*4 + tg
-  const int sub = lane & 7;  // owns 16 of the 128 dims
+  const int tg = lane / LPT;  // token group: rows r*TG + tg
+  const int sub = lane % LPT;  // owns DPT of the 128 dims
   // Register r of the score pass holds token (r ^ perm)*4 + tg: the lane-dependent
   // order lets the cross-lane halving below keep/send fixed registers.
-  const int perm = ((sub >> 2) & 1) * 2 + ((sub >> 1) & 1);
+  const int perm = sub >> 1;
   const int my_j0 = (QH == 4) ? (sub & 1) * 2 : (QH == 2 ? (sub & 1) : 0);
   const bool hi_lane = (sub & 1) != 0;
   // byte offset of this thread's chunk c inside a row of a tile
@@ -252,8 +267,8 @@ paged_decode_kernel(const DecodeParams p) {
   // ---- consumer state ----
   Cursor cur;  // first block of the current segment
   cur.locate(p, prefix, u0);
-  float2 q2[QH][8];
-  float2 acc[QH][8];
+  float2 q2[QH][HP];
+  float2 acc[QH][HP];
   float m_run[NV], l_run[NV];
 
   auto begin_item = [&]() {
@@ -275,7 +290,7 @@ paged_decode_kernel(const DecodeParams p) {
           q2[j][(c * E + e) / 2] = make_float2(f[e] * sc, f[e + 1] * sc);
       }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[j][i] = make_float2(0.f, 0.f);
+      for (int i = 0; i < HP; ++i) acc[j][i] = make_float2(0.f, 0.f);
     }
 #pragma unroll
     for (int k = 0; k < NV; ++k) { m_run[k] = -INFINITY; l_run[k] = 0.f; }
@@ -286,10 +301,10 @@ paged_decode_kernel(const DecodeParams p) {
   auto pv_pass = [&](const uint8_t* vt, const float* pb, int nvalid, auto full_tag) {
     constexpr bool kFull = decltype(full_tag)::value;
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int tok = r * 4 + tg;
+    for (int r = 0; r < R; ++r) {
+      const int tok = r * TG + tg;
       if (kFull || tok < nvalid) {
-        float vf[16];
+        float vf[DPT];
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
           uint4 raw = *reinterpret_cast<const uint4*>(vt + tok * (kD * C::kEltB) + coff[c]);
@@ -309,7 +324,7 @@ paged_decode_kernel(const DecodeParams p) {
         for (int j = 0; j < QH; ++j) {
           const float2 pp = make_float2(pj[j], pj[j]);
 #pragma unroll
-          for (int d = 0; d < 8; ++d)
+          for (int d = 0; d < HP; ++d)
             acc[j][d] = __ffma2_rn(pp, make_float2(vf[2 * d], vf[2 * d + 1]), acc[j][d]);
         }
       }
@@ -322,12 +337,13 @@ paged_decode_kernel(const DecodeParams p) {
 #pragma unroll
     for (int j = 0; j < QH; ++j)
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < HP; ++i) {
         float2 a = acc[j][i];
-        a.x += __shfl_xor_sync(0xffffffffu, a.x, 8);
-        a.y += __shfl_xor_sync(0xffffffffu, a.y, 8);
-        a.x += __shfl_xor_sync(0xffffffffu, a.x, 16);
-        a.y += __shfl_xor_sync(0xffffffffu, a.y, 16);
+#pragma unroll
+        for (int m = LPT; m < 32; m <<= 1) {
+          a.x += __shfl_xor_sync(0xffffffffu, a.x, m);
+          a.y += __shfl_xor_sync(0xffffffffu, a.y, m);
+        }
         acc[j][i] = a;
       }
     float mh[QH], lh[QH];  // running max and sum of every head, in every lane
@@ -355,11 +371,11 @@ paged_decode_kernel(const DecodeParams p) {
       mh[0] = m_run[0];
       lh[0] = l_run[0];
     }
-    // token group tg writes head j == tg (all groups hold the same sums)
+    // token group tg writes the heads j with j % TG == tg (all groups hold the same sums)
 #pragma unroll
     for (int j = 0; j < QH; ++j) {
       const int hq = hg * QH + j;
-      if (tg == (j & 3) && hq < p.kv_mul) {
+      if (tg == (j % TG) && hq < p.kv_mul) {
         if (whole_item) {
           uint8_t* o = reinterpret_cast<uint8_t*>(static_cast<T*>(p.out) + int64_t(item.b) * p.num_q_heads * kD +
                                                   int64_t(item.kvh * p.kv_mul + hq) * kD);
@@ -393,50 +409,40 @@ paged_decode_kernel(const DecodeParams p) {
     // The item is cut by a range boundary.  Publish this piece, then count it; the warp
     // that brings the count up to the number of pieces assembles the item from all of
     // them (nobody waits: whoever arrives last does the work) and resets the counter.
-    __threadfence();
-    __syncwarp();
-    auto owner_of = [&](int64_t u) -> int64_t {
-      int64_t c = (u * W) / total;
-      if (c >= W) c = W - 1;
-      while (c + 1 < W && range_start(total, c + 1, W) <= u) ++c;
-      while (c > 0 && range_start(total, c, W) > u) --c;
-      return c;
-    };
-    const int64_t c_first = owner_of(item_start), c_last = owner_of(item_start + item.nblk - 1);
-    int pieces = 0;
-    for (int64_t c = c_first + lane; c <= c_last; c += 32)
-      pieces += range_start(total, c, W) < range_start(total, c + 1, W) ? 1 : 0;
-#pragma unroll
-    for (int d = 16; d >= 1; d >>= 1) pieces += __shfl_xor_sync(0xffffffffu, pieces, d);
+    __syncwarp();  // every lane's piece is ordered before lane 0's release below
+    // every warp between the owners of the item's first and last block holds a piece of it
+    const int64_t c_first = split.owner(item_start), c_last = split.owner(item_start + item.nblk - 1);
+    const int pieces = int(c_last - c_first) + 1;
     int* cnt = p.counters + (item.b * (p.num_kv_heads * p.head_groups) + item.sub);
     int prev = 0;
-    if (lane == 0) prev = atomicAdd(cnt, 1);
+    if (lane == 0)  // release our piece, acquire the others' (device scope, cumulative over the warp)
+      asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(prev) : "l"(cnt) : "memory");
     prev = __shfl_sync(0xffffffffu, prev, 0);
     if (prev != pieces - 1) return;
     if (lane == 0) *cnt = 0;
-    __threadfence();
-    const int j = tg;  // token group tg assembles head tg; lane `sub` its 16 dims
-    const int hq = hg * QH + j;
-    if (j < QH && hq < p.kv_mul) {
+    __syncwarp();
+    // token group tg assembles the heads j with j % TG == tg; lane `sub` its DPT dims
+    for (int j = tg; j < QH; j += TG) {
+      const int hq = hg * QH + j;
+      if (hq >= p.kv_mul) continue;
       float M = -INFINITY, L = 0.f;
-      float O[16];
+      float O[DPT];
 #pragma unroll
-      for (int e = 0; e < 16; ++e) O[e] = 0.f;
+      for (int e = 0; e < DPT; ++e) O[e] = 0.f;
 #pragma unroll 2
       for (int64_t c = c_first; c <= c_last; ++c) {
-        const int64_t cs = range_start(total, c, W);
-        if (cs >= range_start(total, c + 1, W)) continue;  // that warp had no blocks
-        const float* ps = p.partials + ((item_start < cs) ? 2 * c : 2 * c + 1) * C::kPartialFloats;
+        // only the first piece can be a "tail" slot
+        const float* ps = p.partials + ((c == c_first) ? 2 * c + 1 : 2 * c) * C::kPartialFloats;
         const float mw = __ldcg(ps + QH * kD + j), lw = __ldcg(ps + QH * kD + QH + j);
-        float4 v[4];
+        float4 v[DPT / 4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
+        for (int k = 0; k < DPT / 4; ++k)
           v[k] = __ldcg(reinterpret_cast<const float4*>(ps + j * kD + coff[(k * 4) / E] / C::kEltB + (k * 4) % E));
         const float Mn = fmaxf(M, mw);
         const float a = fast_exp2(M - Mn), bsc = fast_exp2(mw - Mn);
         L = L * a + lw * bsc;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < DPT / 4; ++k) {
           O[4 * k + 0] = O[4 * k + 0] * a + v[k].x * bsc;
           O[4 * k + 1] = O[4 * k + 1] * a + v[k].y * bsc;
           O[4 * k + 2] = O[4 * k + 2] * a + v[k].z * bsc;
@@ -481,13 +487,13 @@ paged_decode_kernel(const DecodeParams p) {
     if (kPend) {
       if (!wait_slot(bars + NS + vs, vph)) return false;
     }
-    float part[4 * QH];
+    float part[R * QH];
     {
       const uint8_t* kt = ring + ks * C::kTileB;
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const uint8_t* krow = kt + ((r ^ perm) * 4 + tg) * (kD * C::kEltB);
-        float kf[16];
+      for (int r = 0; r < R; ++r) {
+        const uint8_t* krow = kt + ((r ^ perm) * TG + tg) * (kD * C::kEltB);
+        float kf[DPT];
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
           uint4 raw = *reinterpret_cast<const uint4*>(krow + coff[c]);
@@ -497,17 +503,20 @@ paged_decode_kernel(const DecodeParams p) {
         for (int j = 0; j < QH; ++j) {
           float2 s2 = make_float2(0.f, 0.f);
 #pragma unroll
-          for (int d = 0; d < 8; ++d)
+          for (int d = 0; d < HP; ++d)
             s2 = __ffma2_rn(q2[j][d], make_float2(kf[2 * d], kf[2 * d + 1]), s2);
           part[r * QH + j] = s2.x + s2.y;
         }
       }
     }
-    // halving: registers r>=2 go to lane^4, then r==1 to lane^2; what is left is token perm*4+tg
+    // halving over the row index: the upper half of the registers goes to lane ^ (LPT/2), then
+    // lane ^ (LPT/4), ... down to lane ^ 2; what is left is token row perm*TG + tg
 #pragma unroll
-    for (int k = 0; k < 2 * QH; ++k) part[k] += __shfl_xor_sync(0xffffffffu, part[2 * QH + k], 4);
+    for (int m = LPT / 2, half = R * QH / 2; m >= 2; m >>= 1, half >>= 1) {
 #pragma unroll
-    for (int k = 0; k < QH; ++k) part[k] += __shfl_xor_sync(0xffffffffu, part[QH + k], 2);
+      for (int k = 0; k < R * QH / 2; ++k)
+        if (k < half) part[k] += __shfl_xor_sync(0xffffffffu, part[half + k], m);
+    }
     if (QH == 4) {
       float s0 = hi_lane ? part[0] : part[2], s1 = hi_lane ? part[1] : part[3];
       float k0 = hi_lane ? part[2] : part[0], k1 = hi_lane ? part[3] : part[1];
@@ -519,7 +528,7 @@ paged_decode_kernel(const DecodeParams p) {
     } else {
       part[0] += __shfl_xor_sync(0xffffffffu, part[0], 1);
     }
-    const bool tok_ok = (perm * 4 + tg) < nvalid;
+    const bool tok_ok = (perm * TG + tg) < nvalid;
     float alpha[NV];
     bool changed = false;
 #pragma unroll
@@ -542,9 +551,9 @@ paged_decode_kernel(const DecodeParams p) {
       pv_pass(ring + (NS + vs) * C::kTileB, p_s + ((i - 1) & 1) * (kBS * 4), kBS, std::true_type{});
     float* pb_new = p_s + (i & 1) * (kBS * 4);
     if (QH == 4) {
-      *reinterpret_cast<float2*>(pb_new + (perm * 4 + tg) * 4 + my_j0) = make_float2(part[0], part[1]);
+      *reinterpret_cast<float2*>(pb_new + (perm * TG + tg) * 4 + my_j0) = make_float2(part[0], part[1]);
     } else {
-      pb_new[(perm * 4 + tg) * 4 + my_j0] = part[0];
+      pb_new[(perm * TG + tg) * 4 + my_j0] = part[0];
     }
     if (__any_sync(0xffffffffu, changed)) {
       float al[QH];
@@ -565,7 +574,7 @@ paged_decode_kernel(const DecodeParams p) {
 #pragma unroll
       for (int j = 0; j < QH; ++j)
 #pragma unroll
-        for (int d = 0; d < 8; ++d) {
+        for (int d = 0; d < HP; ++d) {
           acc[j][d].x *= al[j];
           acc[j][d].y *= al[j];
         }
@@ -586,6 +595,18 @@ paged_decode_kernel(const DecodeParams p) {
   int i = 0;
   while (i < n) {
     const int m = min(n - i, cur.nblk - cur.blk);           // blocks of this item in the range
+    if (i + m < n && lane < QH * 2) {
+      // the next segment starts a new item: pull its query rows towards L2 now (128-byte lines)
+      Cursor nx = cur;
+      nx.blk += m - 1;
+      nx.advance(p, prefix);
+      const int hgn = nx.sub - nx.kvh * p.head_groups;
+      const int hqn = min(hgn * QH + (lane >> 1), p.kv_mul - 1);
+      const uint8_t* qn = static_cast<const uint8_t*>(p.q) +
+                          (int64_t(nx.b) * p.num_q_heads + nx.kvh * p.kv_mul + hqn) * (kD * C::kEltB) +
+                          (lane & 1) * (kD * C::kEltB / 2);
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(qn));
+    }
     const bool to_item_end = (cur.blk + m == cur.nblk);
     const int tail_valid = to_item_end ? cur.len - (cur.nblk - 1) * kBS : kBS;  // tokens in the segment's last block
     if (!step(i, m == 1 ? tail_valid : kBS, std::false_type{})) return;
@@ -632,13 +653,13 @@ constexpr int kStatusBytes = 256;
 // Tuning knob: 0 = default shape; set through kpx_internal_set_decode_variant.
 int g_decode_variant = 0;
 
-template <typename T, int QH, int NW, int NS>
+template <typename T, int QH, int NW, int NS, int LPT>
 int launch_decode(DecodeParams p, cudaStream_t stream) {
-  using C = Cfg<T, QH, NW, NS>;
+  using C = Cfg<T, QH, NW, NS, LPT>;
   static int configured_dev = -1;
   int dev = 0;
   KPX_CUDA_TRY(cudaGetDevice(&dev));
-  auto kern = paged_decode_kernel<T, QH, NW, NS>;
+  auto kern = paged_decode_kernel<T, QH, NW, NS, LPT>;
   if (configured_dev != dev) {
     KPX_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
     configured_dev = dev;
@@ -653,15 +674,16 @@ int launch_decode(DecodeParams p, cudaStream_t stream) {
 
 template <typename T, int QH>
 int launch_shape(const DecodeParams& p, cudaStream_t stream) {
-  if (sizeof(T) == 4) return launch_decode<T, QH, 6, 2>(p, stream);
+  if (sizeof(T) == 4) return launch_decode<T, QH, 6, 2, 8>(p, stream);
   if (sizeof(T) == 2) {
     switch (g_decode_variant) {
-      case 1: return launch_decode<T, QH, 8, 2>(p, stream);
-      case 2: return launch_decode<T, QH, 12, 2>(p, stream);
+      case 1: return launch_decode<T, QH, 8, 3, 8>(p, stream);
+      case 2: return launch_decode<T, QH, 8, 3, 16>(p, stream);
+      case 3: return launch_decode<T, QH, 16, 1, 16>(p, stream);
       default: break;
     }
   }
-  return launch_decode<T, QH, 8, 3>(p, stream);
+  return launch_decode<T, QH, 12, 2, 16>(p, stream);
 }
 
 template <typename T>

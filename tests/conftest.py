@@ -37,6 +37,9 @@ def native_libs():
     so = build.LIB / "libkpx.so"
     if not so.exists() or os.environ.get("KPX_REBUILD"):
         build.build_all()
+    if os.environ.get("KPX_DECODE_VARIANT"):
+        import ctypes
+        ctypes.CDLL(str(so)).kpx_internal_set_decode_variant(int(os.environ["KPX_DECODE_VARIANT"]))
     return so
 
 
