@@ -376,8 +376,8 @@ def run_gpu(args):
 
 # dram bytes (read+write) / algorithmic bytes of one decode launch, from the ncu capture
 # summarised in profiles/ (same kernel, same shape, one layer)
-TRAFFIC_RATIO = 1.019
-TRAFFIC_NOTE = "ncu dram__bytes_read+write of one launch at this shape / algorithmic bytes = 1.019"
+TRAFFIC_RATIO = 1.017
+TRAFFIC_NOTE = "ncu dram__bytes_read+write of one launch at this shape / algorithmic bytes = 1.017"
 
 
 def main():
