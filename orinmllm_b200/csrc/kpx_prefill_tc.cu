@@ -171,10 +171,11 @@ __device__ __forceinline__ float unpack_hi<__half>(uint32_t w) {
 }
 
 constexpr int kSmemBytes = 1024 /*align slack*/ + kOperandB /*Q*/ + 2 * kOperandB /*K x2*/ +
-                           2 * kOperandB /*V x2*/ + 2 * kOperandB /*P, and P_lo for bf16*/ + 64 /*barriers, tmem slot*/;
+                           2 * kOperandB /*V x2*/ + 2 * kOperandB /*P_hi, P_lo*/ + 64 /*barriers, tmem slot*/ +
+                           2 * kTile * 4 /*row maxima of the two column halves*/;
 
 template <typename T>
-__global__ void __launch_bounds__(128, 1) prefill_tc_kernel(const PrefillParams p) {
+__global__ void __launch_bounds__(256, 1) prefill_tc_kernel(const PrefillParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
@@ -184,8 +185,12 @@ __global__ void __launch_bounds__(128, 1) prefill_tc_kernel(const PrefillParams 
   uint64_t* bar_s = reinterpret_cast<uint64_t*>(sP + 2 * kOperandB);
   uint64_t* bar_o = bar_s + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o + 1);
+  float* s_half = reinterpret_cast<float*>(sP + 2 * kOperandB + 64);  // [2][128] exchange between column halves
 
+  // 8 warps: warp w and warp w+4 share TMEM lanes (= query rows) 32*(w&3)..+31; the first owns
+  // columns 0..63 of S and O, the second columns 64..127.
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int row = tid & 127, half = tid >> 7;
   const int head = blockIdx.x % p.num_q_heads;
   const TileDesc td = p.tiles[blockIdx.x / p.num_q_heads];
   const int kvh = head / p.kv_mul;
@@ -205,15 +210,15 @@ __global__ void __launch_bounds__(128, 1) prefill_tc_kernel(const PrefillParams 
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tS = tmem, tO = tmem + 128;
-  const uint32_t lane_addr = uint32_t(warp * 32) << 16;  // this warp's 32 TMEM lanes
+  const uint32_t lane_addr = (uint32_t((warp & 3) * 32) << 16) + uint32_t(half * 64);  // lanes and column half
 
-  // thread t moves 16-byte chunk (t & 15) of rows (t >> 4) + 8*i, i = 0..15
+  // thread t moves 16-byte chunk (t & 15) of rows (t >> 4) + 16*i, i = 0..7
   const int c16 = tid & 15, rbase = tid >> 4;
   {
     const uint8_t* qsrc = static_cast<const uint8_t*>(p.q) + (int64_t(td.row0) * p.num_q_heads + head) * (kD * 2) + c16 * 16;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int r = rbase + 8 * i;
+    for (int i = 0; i < 8; ++i) {
+      const int r = rbase + 16 * i;
       if (r < td.nrows) cp_async16(sQ + swz(r, c16), qsrc + int64_t(r) * p.num_q_heads * (kD * 2));
       else *reinterpret_cast<uint4*>(sQ + swz(r, c16)) = make_uint4(0, 0, 0, 0);
     }
@@ -222,11 +227,11 @@ __global__ void __launch_bounds__(128, 1) prefill_tc_kernel(const PrefillParams 
     uint8_t* dk = sK + buf * kOperandB;
     uint8_t* dv = sV + buf * kOperandB;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int r = rbase + 8 * i;          // key row inside the tile; block (j*8 + i/2) for every thread
+    for (int i = 0; i < 8; ++i) {
+      const int r = rbase + 16 * i;         // key row inside the tile; block j*8 + i for every thread
       const int key = j * kTile + r;
       if (key < kv_len) {
-        int id = __ldg(table + j * (kTile / kBS) + (i >> 1));
+        int id = __ldg(table + j * (kTile / kBS) + i);
         if (id < 0 || (p.num_blocks > 0 && id >= p.num_blocks)) {
           atomicMax(p.status, KPX_ERR_INVALID_ARGUMENT);
           id = 0;
@@ -249,7 +254,7 @@ __global__ void __launch_bounds__(128, 1) prefill_tc_kernel(const PrefillParams 
   // up to a few 1e-3 absolute on short sequences, beyond the 2e-3 / 1e-2 output tolerance, so
   // P is written as two 16-bit terms P = P_hi + P_lo and the output pass runs once per term.
   constexpr bool kSplitP = true;
-  const int my_pos = td.pos0 + tid;  // position of this thread's query row
+  const int my_pos = td.pos0 + row;  // position of this thread's query row
   float m_run = -INFINITY, l_run = 0.f;
   bool failed = false;
 
@@ -277,23 +282,25 @@ __global__ void __launch_bounds__(128, 1) prefill_tc_kernel(const PrefillParams 
     uint32_t r[32];
     float mx = -INFINITY;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < 2; ++c) {
       tmem_ld32(tS + lane_addr + c * 32, r);
 #pragma unroll
       for (int e = 0; e < 32; ++e) {
         float x = __uint_as_float(r[e]) * p.qscale;
-        if (diag && (j * kTile + c * 32 + e) > my_pos) x = -INFINITY;
+        if (diag && (j * kTile + half * 64 + c * 32 + e) > my_pos) x = -INFINITY;
         mx = fmaxf(mx, x);
       }
     }
-    const float m_new = fmaxf(m_run, mx);
+    s_half[half * kTile + row] = mx;
+    __syncthreads();  // the other half of the row has published its maximum
+    const float m_new = fmaxf(m_run, fmaxf(mx, s_half[(half ^ 1) * kTile + row]));
     // rows past the tile's valid rows may see nothing at all: keep them finite
     const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
     const float alpha = fast_exp2(m_run - m_use);
     l_run *= alpha;
     m_run = m_new;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < 2; ++c) {
       tmem_ld32(tS + lane_addr + c * 32, r);
       uint32_t packed[16];
       uint32_t packed_lo[kSplitP ? 16 : 1];
@@ -302,8 +309,8 @@ __global__ void __launch_bounds__(128, 1) prefill_tc_kernel(const PrefillParams 
         float x0 = __uint_as_float(r[e]) * p.qscale, x1 = __uint_as_float(r[e + 1]) * p.qscale;
         float p0 = fast_exp2(x0 - m_use), p1 = fast_exp2(x1 - m_use);
         if (diag) {
-          if ((j * kTile + c * 32 + e) > my_pos) p0 = 0.f;
-          if ((j * kTile + c * 32 + e + 1) > my_pos) p1 = 0.f;
+          if ((j * kTile + half * 64 + c * 32 + e) > my_pos) p0 = 0.f;
+          if ((j * kTile + half * 64 + c * 32 + e + 1) > my_pos) p1 = 0.f;
         }
         l_run += p0 + p1;
         packed[e >> 1] = pack2<T>(p0, p1);
@@ -312,22 +319,22 @@ __global__ void __launch_bounds__(128, 1) prefill_tc_kernel(const PrefillParams 
           packed_lo[e >> 1] = pack2<T>(p0 - unpack_lo<T>(hi), p1 - unpack_hi<T>(hi));
         }
       }
-      // keys c*32 .. c*32+31 of row tid = four 16-byte chunks 4c .. 4c+3 of the row
+      // keys half*64 + c*32 .. +31 of this row = four 16-byte chunks half*8 + 4c .. +3 of the row
 #pragma unroll
       for (int v = 0; v < 4; ++v)
-        *reinterpret_cast<uint4*>(sP + swz(tid, c * 4 + v)) =
+        *reinterpret_cast<uint4*>(sP + swz(row, half * 8 + c * 4 + v)) =
             make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
       if (kSplitP) {
 #pragma unroll
         for (int v = 0; v < 4; ++v)
-          *reinterpret_cast<uint4*>(sP + kOperandB + swz(tid, c * 4 + v)) =
+          *reinterpret_cast<uint4*>(sP + kOperandB + swz(row, half * 8 + c * 4 + v)) =
               make_uint4(packed_lo[4 * v], packed_lo[4 * v + 1], packed_lo[4 * v + 2], packed_lo[4 * v + 3]);
       }
     }
     // ---- rescale O where a running maximum moved (the previous O += P V has completed) ----
     if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         tmem_ld32(tO + lane_addr + c * 32, r);
 #pragma unroll
         for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
@@ -363,13 +370,18 @@ __global__ void __launch_bounds__(128, 1) prefill_tc_kernel(const PrefillParams 
 
   if (!failed) {
     // ---- epilogue: out = O / l ----
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    uint8_t* orow = static_cast<uint8_t*>(p.out) + (int64_t(td.row0 + tid) * p.num_q_heads + head) * (kD * 2);
+    // the row sum is the sum of the two column halves
+    s_half[half * kTile + row] = l_run;
+    __syncthreads();
+    const float l_row = l_run + s_half[(half ^ 1) * kTile + row];
+    const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+    uint8_t* orow = static_cast<uint8_t*>(p.out) + (int64_t(td.row0 + row) * p.num_q_heads + head) * (kD * 2) +
+                    half * 128;
     uint32_t r[32];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < 2; ++c) {
       tmem_ld32(tO + lane_addr + c * 32, r);
-      if (tid < td.nrows) {
+      if (row < td.nrows) {
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
           uint4 w;
@@ -434,7 +446,7 @@ int prefill_tc(void* out, const void* q, const void* k_pool, const void* v_pool,
       KPX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
       done = dev;
     }
-    prefill_tc_kernel<__half><<<grid, 128, kSmemBytes, stream>>>(p);
+    prefill_tc_kernel<__half><<<grid, 256, kSmemBytes, stream>>>(p);
   } else {
     static int done = -1;
     int dev = 0;
@@ -443,7 +455,7 @@ int prefill_tc(void* out, const void* q, const void* k_pool, const void* v_pool,
       KPX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
       done = dev;
     }
-    prefill_tc_kernel<__nv_bfloat16><<<grid, 128, kSmemBytes, stream>>>(p);
+    prefill_tc_kernel<__nv_bfloat16><<<grid, 256, kSmemBytes, stream>>>(p);
   }
   return cuda_status(cudaGetLastError());
 }
