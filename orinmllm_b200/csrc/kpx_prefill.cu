@@ -48,6 +48,12 @@ extern "C" __attribute__((visibility("default"))) void kpx_internal_set_prefill_
   g_prefill_path = v;
 }
 
+// Work list of the tensor-core path: at most one 40-byte entry per (128-row query tile, query
+// head), and there are never more tiles than query tokens.
+static int64_t tile_area_bytes(int32_t total_q, int32_t num_q_heads) {
+  return align256((int64_t(total_q) + 1) * int64_t(num_q_heads > 0 ? num_q_heads : 1) * 40);
+}
+
 extern "C" int64_t kpx_prefill_workspace_bytes(int32_t total_q, int32_t num_q_heads,
                                                int32_t num_kv_heads, int32_t head_size) {
   if (total_q < 0) return -1;
@@ -55,7 +61,7 @@ extern "C" int64_t kpx_prefill_workspace_bytes(int32_t total_q, int32_t num_q_he
   if (dec < 0) return -1;
   // decode workspace, then lens[total_q], rows[total_q], cu[<=total_q+1], start[<=total_q]
   return dec + align256(int64_t(total_q) * 4) * 2 + align256((int64_t(total_q) + 1) * 4) * 2 +
-         align256((int64_t(total_q) + 1) * 16);  // + tile list of the tensor-core path
+         tile_area_bytes(total_q, num_q_heads);  // + work list of the tensor-core path
 }
 
 extern "C" int kpx_paged_prefill(void* out, const void* q, const void* k_pool, const void* v_pool,
@@ -92,7 +98,7 @@ extern "C" int kpx_paged_prefill(void* out, const void* q, const void* k_pool, c
     uint8_t* tile_area = base + 2 * align256(int64_t(total_q) * 4) + 2 * align256((int64_t(total_q) + 1) * 4);
     int rc = prefill_tc(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq, cu_q_lens_host,
                         start_pos_host, batch, num_q_heads, scale, tile_area,
-                        align256((int64_t(total_q) + 1) * 16), static_cast<int32_t*>(workspace), s);
+                        tile_area_bytes(total_q, num_q_heads), static_cast<int32_t*>(workspace), s);
     if (rc != KPX_ERR_UNIMPLEMENTED) return rc;
   }
   KPX_CUDA_TRY(cudaMemcpyAsync(cu, cu_q_lens_host, size_t(batch + 1) * 4, cudaMemcpyHostToDevice, s));

@@ -1,19 +1,22 @@
 // Chunked-prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM), 16-bit caches.
 //
-// One CTA = one tile of 128 query rows of one query head of one sequence.  Q, K, V and the
-// softmax weights P live in shared memory in the 128-byte-swizzled layouts the UMMA shared
-// memory descriptors describe; S = Q K^T (128x128 fp32) and the output accumulator O
-// (128x128 fp32) live in tensor memory (256 columns).  Per 128-key tile:
-//     tcgen05.mma  S  = Q  . K^T          (K-major A and B, 8 steps of k = 16 over d = 128)
-//     threads      P  = exp2(S*c - m)     one query row per thread (TMEM lane == row),
-//                                          read with tcgen05.ld, causal mask on the diagonal
-//     tcgen05.mma  O += P . V             (A = P K-major, B = V MN-major as it sits in the pool)
-// O is rescaled in TMEM (tcgen05.ld / st) only when a row's running maximum moved.  K/V tiles
-// are gathered through the block table with cp.async into the swizzled layout (the next tile
-// is in flight while the current one is being used); the pool's [16 tokens][128] tiles are
-// already row-contiguous, so paging costs nothing extra.
-// Every mbarrier wait is bounded and voted on by the whole CTA, so a wait that gives up ends
-// the CTA in step (TMEM is freed on every path) and raises the workspace status word.
+// One CTA = two items (128 query rows x one query head each) of one sequence that share a KV
+// head, so one stream of K/V tiles serves both.  Roles:
+//   warp 9       TMA: Q boxes, then per 128-key tile the (block, head) boxes of K and V through
+//                the block table into 128-byte-swizzled shared memory (two stages each)
+//   warp 8       one thread issues tcgen05.mma:  S_x = Q_x K^T  into tensor memory (128 columns
+//                per item) and  O_x += P_x V  (A = P read from tensor memory, B = V MN-major
+//                as it sits in the pool); completion is committed to mbarriers
+//   warps 0..7   softmax: S_x -> P_x = exp2(S*c - m) written over S_x as two 16-bit terms
+//                (tcgen05.ld / st; two threads per query row), causal mask on the diagonal,
+//                running maximum moved lazily, O_x rescaled in tensor memory when it moves
+// The MMA order  PV_0(j) QK_0(j+1) | PV_1(j) QK_1(j+1)  keeps the tensor core on one item while
+// the softmax threads work on the other.
+// Every mbarrier wait is bounded; a role that gives up raises a CTA-wide flag that ends the
+// other roles' waits, TMEM is freed on every path and the workspace status word is raised.
+#include <cuda.h>  // CUtensorMap and the enums of cuTensorMapEncodeTiled (types only; no libcuda link)
+
+#include <algorithm>
 #include <vector>
 
 #include "kpx_common.cuh"
@@ -26,34 +29,32 @@ constexpr int kChunkB = kTile * 128;      // one 64-element-wide column slab: 12
 constexpr int kOperandB = 2 * kChunkB;    // a 128 x 128 16-bit operand tile
 constexpr float kLog2e = 1.4426950408889634f;
 
-struct TileDesc {
-  int32_t seq;    // row of the block table
+// One unit of work: 128 query rows of one query head.
+struct ItemDesc {
   int32_t row0;   // first query row (global) of the tile
-  int32_t nrows;  // valid rows (<= 128)
+  int32_t nrows;  // valid rows (<= 128); 0 = no item
   int32_t pos0;   // cache position of row0
+  int32_t head;   // query head
+};
+// One CTA: two items of one sequence that share a KV head, so that one stream of K/V tiles
+// serves both.  it[1] is always present and sees at least as many keys as it[0].
+struct PairDesc {
+  int32_t seq;  // row of the block table
+  int32_t kvh;
+  ItemDesc it[2];
 };
 
 struct PrefillParams {
   void* out;
-  const void* q;
-  const uint8_t* k_pool;
-  const uint8_t* v_pool;
   const int32_t* block_table;
-  const TileDesc* tiles;
+  const PairDesc* pairs;
   int32_t* status;
-  int64_t block_stride_b, head_stride_b;
   int64_t num_blocks;
   int32_t max_blocks_per_seq, num_q_heads, kv_mul;
   float qscale;  // softmax scale * log2(e)
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------------
-__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() {
-  asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
-}
 __device__ __forceinline__ void fence_async_proxy() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -85,6 +86,24 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
+// D[tmem] (+)= A[tmem] * B[smem]: A is read from tensor memory (row = lane, two 16-bit k values
+// per 32-bit column, 8 columns per k = 16 step)
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -128,11 +147,6 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t a_format, uint32_t b_
          ((128u >> 4) << 24);
 }
 
-// Byte offset of (row, 16-byte chunk c16 of the 256-byte row) inside a swizzled 128x128 tile.
-__device__ __forceinline__ int swz(int row, int c16) {
-  return (c16 >> 3) * kChunkB + row * 128 + (((c16 & 7) ^ (row & 7)) << 4);
-}
-
 template <typename T>
 struct Fmt;
 template <>
@@ -170,294 +184,534 @@ __device__ __forceinline__ float unpack_hi<__half>(uint32_t w) {
   return __half2float(__ushort_as_half(static_cast<unsigned short>(w >> 16)));
 }
 
-constexpr int kSmemBytes = 1024 /*align slack*/ + kOperandB /*Q*/ + 2 * kOperandB /*K x2*/ +
-                           2 * kOperandB /*V x2*/ + 2 * kOperandB /*P_hi, P_lo*/ + 64 /*barriers, tmem slot*/ +
-                           2 * kTile * 4 /*row maxima of the two column halves*/;
+
+// Tensor memory is allocated per CTA and the occupancy calculator places one CTA of this kernel
+// per SM whatever its shared-memory and register footprint, so the overlap of softmax and
+// tensor-core work has to happen inside the CTA: each CTA carries two items (A, B) and
+// alternates between them.
+constexpr int kMmaWarp = 8, kLoadWarp = 9;  // warps 0..7 run the softmax
+constexpr int kThreads = 320;
+constexpr int kSmemBytes = 1024 /*align slack*/ + 2 * kOperandB /*Q of A, B*/ + 2 * kOperandB /*K x2*/ +
+                           2 * kOperandB /*V x2*/ + 256 /*barriers, tmem slot, abort flag*/ +
+                           2 * kTile * 4 /*exchange between the two column halves of a row*/;
+
+// Barrier among the 256 softmax threads only (hardware barrier 1; barrier 0 is __syncthreads).
+__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// The same with a vote: true when any of the 256 threads passes true.
+__device__ __forceinline__ bool softmax_sync_or(bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\t"
+      "bar.red.or.pred q, 1, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"(uint32_t(pred))
+      : "memory");
+  return out != 0;
+}
+// Bounded wait that also gives up as soon as another role of the CTA has given up.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) {
+      __nanosleep(64);
+      if ((i & 127) == 0 && *abort_flag) return false;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+// Tiled TMA loads (no multicast): a box of the tensor map lands in shared memory, 128-byte
+// swizzled, and its bytes are counted on the mbarrier.
+__device__ __forceinline__ void tma_load_3d(void* dst, const void* tmap, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(dst)), "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* dst, const void* tmap, int c0, int c1, int c2, int c3,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], "
+      "[%6];"
+      ::"r"(smem_u32(dst)), "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t addr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+      "%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Largest of 32 scores; with kMasked, scores of keys e > limit (newer than the query) do not count.
+template <bool kMasked>
+__device__ __forceinline__ float max32(const uint32_t* r, int limit, float mx) {
+#pragma unroll
+  for (int e = 0; e < 32; e += 2) {
+    float a = __uint_as_float(r[e]), b = __uint_as_float(r[e + 1]);
+    if (kMasked) {
+      if (e > limit) a = -INFINITY;
+      if (e + 1 > limit) b = -INFINITY;
+    }
+    mx = fmaxf(mx, fmaxf(a, b));
+  }
+  return mx;
+}
+
+// Weights of 32 keys: p = exp2(s * qscale - m), written back over the 32 columns of S they came
+// from as P_hi (16 columns, two keys each) and P_lo = p - P_hi (16 columns); lsum += p.
+template <typename T, bool kMasked>
+__device__ __forceinline__ void weights32(uint32_t taddr, const uint32_t* r, float qscale, float neg_m, int limit,
+                                          float2& lsum) {
+  uint32_t hi[16], lo[16];
+  const float2 sc = make_float2(qscale, qscale), nm = make_float2(neg_m, neg_m), m1 = make_float2(-1.f, -1.f);
+#pragma unroll
+  for (int e = 0; e < 32; e += 2) {
+    const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), sc, nm);
+    float2 w = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+    if (kMasked) {
+      if (e > limit) w.x = 0.f;
+      if (e + 1 > limit) w.y = 0.f;
+    }
+    lsum = __fadd2_rn(lsum, w);
+    const uint32_t h = pack2<T>(w.x, w.y);
+    hi[e >> 1] = h;
+    const float2 d = __ffma2_rn(make_float2(unpack_lo<T>(h), unpack_hi<T>(h)), m1, w);
+    lo[e >> 1] = pack2<T>(d.x, d.y);
+  }
+  tmem_st16(taddr, hi);
+  tmem_st16(taddr + 16, lo);
+}
+
+// Per-thread softmax state of one item: this thread owns (row, column half) of S and O.
+struct RowState {
+  float m = -INFINITY;            // running maximum (scaled scores), moved lazily
+  float2 l = {0.f, 0.f};          // running sum of weights, as an even/odd pair
+};
+
+// A running maximum is only moved when the tile's maximum exceeds it by more than this (in
+// log2 units): weights stay below 2^8, and O is rescaled in far fewer tiles.
+constexpr float kLazyMax = 8.f;
+
+// Softmax of tile j of one item: S (tensor memory, 128 columns at tS) -> P over S, O rescaled
+// where the row maximum moved.  Called by the 256 softmax threads (contains their barrier).
+template <typename T>
+__device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t lane_addr, int row, int half,
+                                             float qscale, int j, int pos0, float* s_half, RowState& st) {
+  const int my_pos = pos0 + row;
+  const bool diag = (j * kTile + kTile - 1) > pos0;  // some row of this item is masked in this tile
+  const int limit0 = my_pos - (j * kTile + half * 64);   // keys e > limit are newer than the query
+  uint32_t r0[32], r1[32];
+  tmem_ld32_nowait(tS + lane_addr, r0);
+  tmem_ld32_nowait(tS + lane_addr + 32, r1);
+  tmem_wait_ld();
+  float mx;
+  if (diag) mx = max32<true>(r1, limit0 - 32, max32<true>(r0, limit0, -INFINITY));
+  else mx = max32<false>(r1, 0, max32<false>(r0, 0, -INFINITY));
+  s_half[half * kTile + row] = mx;
+  softmax_sync();  // the other half of the row has published its maximum
+  const float m_tile = fmaxf(mx, s_half[(half ^ 1) * kTile + row]) * qscale;
+  float alpha = 1.f;
+  if (m_tile > st.m + kLazyMax || st.m == -INFINITY) {  // (-inf + 8 is -inf: the first tile always moves it)
+    const float m_new = (m_tile == -INFINITY) ? 0.f : m_tile;
+    alpha = fast_exp2(st.m - m_new);
+    st.m = m_new;
+    st.l.x *= alpha;
+    st.l.y *= alpha;
+  }
+  const float neg_m = -st.m;
+  if (diag) {
+    weights32<T, true>(tS + lane_addr, r0, qscale, neg_m, limit0, st.l);
+    weights32<T, true>(tS + lane_addr + 32, r1, qscale, neg_m, limit0 - 32, st.l);
+  } else {
+    weights32<T, false>(tS + lane_addr, r0, qscale, neg_m, 0, st.l);
+    weights32<T, false>(tS + lane_addr + 32, r1, qscale, neg_m, 0, st.l);
+  }
+  // O += P V of the previous tile has completed (the MMA that produced S was issued after it)
+  if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      tmem_ld32(tO + lane_addr + c * 32, r0);
+#pragma unroll
+      for (int e = 0; e < 32; ++e) r0[e] = __float_as_uint(__uint_as_float(r0[e]) * alpha);
+      tmem_st32(tO + lane_addr + c * 32, r0);
+    }
+  }
+  tmem_wait_st();
+}
+
+// out rows of one item = O / l.  Called by the 256 softmax threads (contains their barrier).
+template <typename T>
+__device__ __forceinline__ void write_item(uint32_t tO, uint32_t lane_addr, int row, int half, const ItemDesc& it,
+                                           int num_q_heads, void* out, float* s_half, const RowState& st) {
+  const float l_mine = st.l.x + st.l.y;
+  softmax_sync();  // earlier readers of the exchange area are done
+  s_half[half * kTile + row] = l_mine;
+  softmax_sync();
+  const float l_row = l_mine + s_half[(half ^ 1) * kTile + row];
+  const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+  uint8_t* orow = static_cast<uint8_t*>(out) + (int64_t(it.row0 + row) * num_q_heads + it.head) * (kD * 2) + half * 128;
+  uint32_t r[32];
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    tmem_ld32(tO + lane_addr + c * 32, r);
+    if (row < it.nrows) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        uint4 w;
+        w.x = pack2<T>(__uint_as_float(r[8 * v + 0]) * inv, __uint_as_float(r[8 * v + 1]) * inv);
+        w.y = pack2<T>(__uint_as_float(r[8 * v + 2]) * inv, __uint_as_float(r[8 * v + 3]) * inv);
+        w.z = pack2<T>(__uint_as_float(r[8 * v + 4]) * inv, __uint_as_float(r[8 * v + 5]) * inv);
+        w.w = pack2<T>(__uint_as_float(r[8 * v + 6]) * inv, __uint_as_float(r[8 * v + 7]) * inv);
+        *reinterpret_cast<uint4*>(orow + (c * 4 + v) * 16) = w;
+      }
+    }
+  }
+}
 
 template <typename T>
-__global__ void __launch_bounds__(256, 1) prefill_tc_kernel(const PrefillParams p) {
+__global__ void __launch_bounds__(kThreads, 1)
+    prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q,
+                      const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sK = sQ + kOperandB;       // two buffers
-  uint8_t* sV = sK + 2 * kOperandB;   // two buffers
-  uint8_t* sP = sV + 2 * kOperandB;
-  uint64_t* bar_s = reinterpret_cast<uint64_t*>(sP + 2 * kOperandB);
-  uint64_t* bar_o = bar_s + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o + 1);
-  float* s_half = reinterpret_cast<float*>(sP + 2 * kOperandB + 64);  // [2][128] exchange between column halves
+  uint8_t* sQ = smem;                  // Q of item 0, Q of item 1
+  uint8_t* sK = sQ + 2 * kOperandB;    // two stages
+  uint8_t* sV = sK + 2 * kOperandB;    // two stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * kOperandB);
+  uint64_t* q_full = bars;         // Q of both items has landed
+  uint64_t* k_full = bars + 1;     // [2] stage holds K(j)
+  uint64_t* v_full = bars + 3;     // [2] stage holds V(j)
+  uint64_t* k_free = bars + 5;     // [2] every MMA reading the stage has completed
+  uint64_t* v_free = bars + 7;     // [2]
+  uint64_t* s_full = bars + 9;     // [2] S of item x complete (and every earlier MMA)
+  uint64_t* p_full = bars + 11;    // [2] P of item x written, O rescaled (8 warps arrive)
+  uint64_t* o_full = bars + 13;    // [2] last O += P V of item x complete
+  uint64_t* tail_ok = bars + 15;   // rows past the newest token are zero in the last V tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
+  float* s_half = reinterpret_cast<float*>(sV + 2 * kOperandB + 256);  // [2][128]
 
-  // 8 warps: warp w and warp w+4 share TMEM lanes (= query rows) 32*(w&3)..+31; the first owns
-  // columns 0..63 of S and O, the second columns 64..127.
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int row = tid & 127, half = tid >> 7;
-  const int head = blockIdx.x % p.num_q_heads;
-  const TileDesc td = p.tiles[blockIdx.x / p.num_q_heads];
-  const int kvh = head / p.kv_mul;
-  const int32_t* table = p.block_table + int64_t(td.seq) * p.max_blocks_per_seq;
-  const int last_pos = td.pos0 + td.nrows - 1;      // newest position any row of the tile may see
-  const int n_tiles = last_pos / kTile + 1;         // key tiles 0 .. n_tiles-1
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const PairDesc pd = p.pairs[blockIdx.x];
+  const int last_pos = pd.it[1].pos0 + pd.it[1].nrows - 1;  // newest position any row of the pair may see
   const int kv_len = last_pos + 1;
+  const int nB = last_pos / kTile + 1;                       // key tiles 0 .. nB-1
+  const int nA = pd.it[0].nrows > 0 ? (pd.it[0].pos0 + pd.it[0].nrows - 1) / kTile + 1 : 0;  // <= nB
+  const bool ragged = (kv_len % kTile) != 0;                 // the last tile has rows past the newest token
 
   if (tid == 0) {
-    mbar_init(bar_s, 1);
-    mbar_init(bar_o, 1);
+    for (int i = 0; i < 16; ++i) mbar_init(bars + i, (i == 11 || i == 12) ? 8u : 1u);
+    *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 0) tmem_alloc(tmem_slot, 256);
+  if (warp == 0) tmem_alloc(tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem, tO = tmem + 128;
-  const uint32_t lane_addr = (uint32_t((warp & 3) * 32) << 16) + uint32_t(half * 64);  // lanes and column half
+  const uint32_t tmem = *tmem_slot;  // columns: S of item 0, S of item 1, O of item 0, O of item 1
 
-  // thread t moves 16-byte chunk (t & 15) of rows (t >> 4) + 16*i, i = 0..7
-  const int c16 = tid & 15, rbase = tid >> 4;
-  {
-    const uint8_t* qsrc = static_cast<const uint8_t*>(p.q) + (int64_t(td.row0) * p.num_q_heads + head) * (kD * 2) + c16 * 16;
+  if (warp == kLoadWarp) {
+    // ===== loader: TMA boxes of Q, then of K(j), V(j) through the block table =====
+    const int32_t* table = p.block_table + int64_t(pd.seq) * p.max_blocks_per_seq;
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, (nA > 0 ? 2u : 1u) * kOperandB);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int r = rbase + 16 * i;
-      if (r < td.nrows) cp_async16(sQ + swz(r, c16), qsrc + int64_t(r) * p.num_q_heads * (kD * 2));
-      else *reinterpret_cast<uint4*>(sQ + swz(r, c16)) = make_uint4(0, 0, 0, 0);
+      for (int x = 0; x < 2; ++x)
+        if (pd.it[x].nrows > 0) {
+          tma_load_3d(sQ + x * kOperandB, &map_q, 0, pd.it[x].head, pd.it[x].row0, q_full);
+          tma_load_3d(sQ + x * kOperandB + kChunkB, &map_q, 64, pd.it[x].head, pd.it[x].row0, q_full);
+        }
     }
-  }
-  auto load_kv = [&](int j, int buf) {
-    uint8_t* dk = sK + buf * kOperandB;
-    uint8_t* dv = sV + buf * kOperandB;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int r = rbase + 16 * i;         // key row inside the tile; block j*8 + i for every thread
-      const int key = j * kTile + r;
-      if (key < kv_len) {
-        int id = __ldg(table + j * (kTile / kBS) + i);
+    bool ok = true;
+    for (int j = 0; j < nB && ok; ++j) {
+      const int stage = j & 1, use = j >> 1;
+      const int left = kv_len - j * kTile;                        // tokens from the start of this tile
+      const int nblk = left >= kTile ? kTile / kBS : (left + kBS - 1) / kBS;
+      // lanes 0..15: block (lane >> 1), 64-element slab (lane & 1)
+      int id = 0;
+      if (lane < 2 * nblk) {
+        id = __ldg(table + j * (kTile / kBS) + (lane >> 1));
         if (id < 0 || (p.num_blocks > 0 && id >= p.num_blocks)) {
           atomicMax(p.status, KPX_ERR_INVALID_ARGUMENT);
           id = 0;
         }
-        const int64_t off = int64_t(id) * p.block_stride_b + int64_t(kvh) * p.head_stride_b + (r & 15) * (kD * 2) + c16 * 16;
-        cp_async16(dk + swz(r, c16), p.k_pool + off);
-        cp_async16(dv + swz(r, c16), p.v_pool + off);
-      } else {  // beyond the newest token: zeros (a weight of 0 times pool garbage must stay 0)
-        *reinterpret_cast<uint4*>(dk + swz(r, c16)) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(dv + swz(r, c16)) = make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int kv = 0; kv < 2; ++kv) {
+        uint64_t* full = (kv ? v_full : k_full) + stage;
+        uint64_t* free_bar = (kv ? v_free : k_free) + stage;
+        if (use > 0) ok = ok && wait_or_abort(free_bar, uint32_t((use - 1) & 1), abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane == 0) mbar_arrive_expect_tx(full, uint32_t(nblk) * (kBS * kD * 2));
+        __syncwarp();
+        if (lane < 2 * nblk) {
+          uint8_t* dst = (kv ? sV : sK) + stage * kOperandB + (lane & 1) * kChunkB + (lane >> 1) * (kBS * 128);
+          tma_load_4d(dst, kv ? &map_v : &map_k, (lane & 1) * 64, 0, pd.kvh, id, full);
+        }
+      }
+      if (ok && ragged && j == nB - 1) {
+        // V rows past the newest token must be zero (a weight of 0 times pool garbage must stay
+        // 0); the boxes have to land first because the last one covers some of these rows
+        ok = wait_or_abort(v_full + stage, uint32_t(use & 1), abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+          uint8_t* v = sV + stage * kOperandB;
+          for (int i = left * 16 + lane; i < kTile * 16; i += 32) {  // 16-byte pieces of rows left..127
+            const int r = i >> 4, c = i & 15;
+            *reinterpret_cast<uint4*>(v + (c >> 3) * kChunkB + r * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+          }
+          fence_async_proxy();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tail_ok);
+        }
       }
     }
-  };
-  load_kv(0, 0);
-
-  constexpr uint32_t kIdescQK = instr_desc(Fmt<T>::kCode, Fmt<T>::kCode, 0);
-  constexpr uint32_t kIdescPV = instr_desc(Fmt<T>::kCode, Fmt<T>::kCode, 1);
-  // A and B of one MMA must have the same 16-bit format (an fp16 P against a bf16 V is an
-  // illegal instruction).  A single 16-bit P (2^-9 rounding for bf16, 2^-12 for fp16) costs
-  // up to a few 1e-3 absolute on short sequences, beyond the 2e-3 / 1e-2 output tolerance, so
-  // P is written as two 16-bit terms P = P_hi + P_lo and the output pass runs once per term.
-  constexpr bool kSplitP = true;
-  const int my_pos = td.pos0 + row;  // position of this thread's query row
-  float m_run = -INFINITY, l_run = 0.f;
-  bool failed = false;
-
-  for (int j = 0; j < n_tiles; ++j) {
-    const int buf = j & 1;
-    cp_async_wait_all();
-    fence_async_proxy();
-    tc_fence_before();
-    __syncthreads();  // tile j (and Q) visible to the tensor core; everybody is done with iteration j-1
-    if (tid == 0) {
+  } else if (warp == kMmaWarp) {
+    // ===== MMA issue: one thread =====
+    if (lane == 0) {
+      constexpr uint32_t kIdescQK = instr_desc(Fmt<T>::kCode, Fmt<T>::kCode, 0);
+      constexpr uint32_t kIdescPV = instr_desc(Fmt<T>::kCode, Fmt<T>::kCode, 1);
+      // descriptors of the operand bases; the k steps add to the 16-byte-unit address field
+      const uint64_t dq[2] = {smem_desc(sQ, 0, 1024), smem_desc(sQ + kOperandB, 0, 1024)};
+      const uint64_t dk[2] = {smem_desc(sK, 0, 1024), smem_desc(sK + kOperandB, 0, 1024)};
+      const uint64_t dv[2] = {smem_desc(sV, kChunkB, 1024), smem_desc(sV + kOperandB, kChunkB, 1024)};
+      bool ok = true;
+      // S_x = Q_x K(j)^T: 8 steps of k = 16 over d = 128 (4 steps per 64-element slab)
+      auto issue_qk = [&](int x, int j) {
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          const uint64_t o = uint64_t(((s >> 2) * kChunkB + (s & 3) * 32) >> 4);
+          umma_f16(tmem + x * 128, dq[x] + o, dk[j & 1] + o, kIdescQK, s > 0);
+        }
+        umma_commit(s_full + x);
+      };
+      // O_x += P_hi V(j) + P_lo V(j).  A = P from tensor memory: keys 16s.. of every row sit in 8
+      // columns; B = V: key rows 16s.., d along MN.  A and B of one MMA must have the same
+      // 16-bit format (an fp16 P against a bf16 V is an illegal instruction).  A single 16-bit P
+      // (2^-9 rounding for bf16, 2^-12 for fp16) costs up to a few 1e-3 absolute on short
+      // sequences, beyond the 2e-3 / 1e-2 output tolerance, hence the two terms.
+      auto issue_pv = [&](int x, int j) {
+        const uint32_t tP = tmem + x * 128, tO = tmem + 256 + x * 128;
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          umma_f16_ts(tO, tP + (s >> 1) * 32 + (s & 1) * 8, dv[j & 1] + uint64_t((s * 16 * 128) >> 4), kIdescPV,
+                      (j > 0 || s > 0) ? 1u : 0u);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          umma_f16_ts(tO, tP + (s >> 1) * 32 + 16 + (s & 1) * 8, dv[j & 1] + uint64_t((s * 16 * 128) >> 4), kIdescPV, 1u);
+      };
+      auto wait = [&](uint64_t* bar, int parity) {
+        ok = ok && wait_or_abort(bar, uint32_t(parity), abort_flag);
+        tc_fence_after();
+        return ok;
+      };
+      // K(j) / V(j) of stage j&1 are in their (j>>1)-th use; the last tile also waits for the zeroed tail
+      auto wait_k = [&](int j) { return wait(k_full + (j & 1), (j >> 1) & 1); };
+      auto wait_v = [&](int j) {
+        if (ragged && j == nB - 1 && !wait(tail_ok, 0)) return false;
+        return wait(v_full + (j & 1), (j >> 1) & 1);
+      };
+      if (wait(q_full, 0) && wait_k(0)) {
+        if (nA > 0) issue_qk(0, 0);
+        issue_qk(1, 0);
+        umma_commit(k_free);
+      }
+      for (int j = 0; j < nB && ok; ++j) {
+        // item 0, while the softmax threads are busy with item 1 (and the other way round below)
+        if (j < nA) {
+          if (!wait(p_full, j & 1) || !wait_v(j)) break;
+          issue_pv(0, j);
+          if (j + 1 == nA) umma_commit(o_full);
+        }
+        if (j + 1 < nA) {
+          if (!wait_k(j + 1)) break;
+          issue_qk(0, j + 1);
+        }
+        if (!wait(p_full + 1, j & 1) || !wait_v(j)) break;
+        issue_pv(1, j);
+        umma_commit(v_free + (j & 1));
+        if (j + 1 == nB) {
+          umma_commit(o_full + 1);
+        } else {
+          if (!wait_k(j + 1)) break;
+          issue_qk(1, j + 1);
+          umma_commit(k_free + ((j + 1) & 1));
+        }
+      }
+    }
+  } else {
+    // ===== softmax: 8 warps; warp w and warp w+4 share TMEM lanes (= query rows) 32*(w&3)..+31,
+    // the first owns columns 0..63 of S and O, the second columns 64..127 =====
+    const int row = tid & 127, half = tid >> 7;
+    const uint32_t lane_addr = (uint32_t((warp & 3) * 32) << 16) + uint32_t(half * 64);
+    RowState st[2];
+    bool failed = false;
+    auto wait_all = [&](uint64_t* bar, int parity) {
+      const bool bad = !wait_or_abort(bar, uint32_t(parity), abort_flag);
+      if (softmax_sync_or(bad)) failed = true;
       tc_fence_after();
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const int o = (k >> 2) * kChunkB + (k & 3) * 32;
-        umma_f16(tS, smem_desc(sQ + o, 0, 1024), smem_desc(sK + buf * kOperandB + o, 0, 1024), kIdescQK, k > 0);
+      return !failed;
+    };
+    auto publish_p = [&](int x) {  // this warp's part of P_x is in tensor memory
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full + x);
+    };
+    for (int j = 0; j < nB; ++j) {
+      if (j < nA) {
+        if (!wait_all(s_full, j & 1)) break;
+        softmax_tile<T>(tmem, tmem + 256, lane_addr, row, half, p.qscale, j, pd.it[0].pos0, s_half, st[0]);
+        publish_p(0);
+      } else if (j == nA && nA > 0) {
+        if (!wait_all(o_full, 0)) break;
+        write_item<T>(tmem + 256, lane_addr, row, half, pd.it[0], p.num_q_heads, p.out, s_half, st[0]);
       }
-      umma_commit(bar_s);
+      if (!wait_all(s_full + 1, j & 1)) break;
+      softmax_tile<T>(tmem + 128, tmem + 384, lane_addr, row, half, p.qscale, j, pd.it[1].pos0, s_half, st[1]);
+      publish_p(1);
     }
-    if (j + 1 < n_tiles) load_kv(j + 1, buf ^ 1);  // in flight during the softmax below
-    failed = !mbar_wait_bounded(bar_s, j & 1);
-    if (__syncthreads_or(failed)) { failed = true; break; }
-    tc_fence_after();
-    // ---- softmax of this thread's row ----
-    const bool diag = (j * kTile + kTile - 1) > td.pos0;  // some row of the tile is masked here
-    uint32_t r[32];
-    float mx = -INFINITY;
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      tmem_ld32(tS + lane_addr + c * 32, r);
-#pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        float x = __uint_as_float(r[e]) * p.qscale;
-        if (diag && (j * kTile + half * 64 + c * 32 + e) > my_pos) x = -INFINITY;
-        mx = fmaxf(mx, x);
-      }
-    }
-    s_half[half * kTile + row] = mx;
-    __syncthreads();  // the other half of the row has published its maximum
-    const float m_new = fmaxf(m_run, fmaxf(mx, s_half[(half ^ 1) * kTile + row]));
-    // rows past the tile's valid rows may see nothing at all: keep them finite
-    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-    const float alpha = fast_exp2(m_run - m_use);
-    l_run *= alpha;
-    m_run = m_new;
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      tmem_ld32(tS + lane_addr + c * 32, r);
-      uint32_t packed[16];
-      uint32_t packed_lo[kSplitP ? 16 : 1];
-#pragma unroll
-      for (int e = 0; e < 32; e += 2) {
-        float x0 = __uint_as_float(r[e]) * p.qscale, x1 = __uint_as_float(r[e + 1]) * p.qscale;
-        float p0 = fast_exp2(x0 - m_use), p1 = fast_exp2(x1 - m_use);
-        if (diag) {
-          if ((j * kTile + half * 64 + c * 32 + e) > my_pos) p0 = 0.f;
-          if ((j * kTile + half * 64 + c * 32 + e + 1) > my_pos) p1 = 0.f;
-        }
-        l_run += p0 + p1;
-        packed[e >> 1] = pack2<T>(p0, p1);
-        if (kSplitP) {
-          const uint32_t hi = packed[e >> 1];
-          packed_lo[e >> 1] = pack2<T>(p0 - unpack_lo<T>(hi), p1 - unpack_hi<T>(hi));
-        }
-      }
-      // keys half*64 + c*32 .. +31 of this row = four 16-byte chunks half*8 + 4c .. +3 of the row
-#pragma unroll
-      for (int v = 0; v < 4; ++v)
-        *reinterpret_cast<uint4*>(sP + swz(row, half * 8 + c * 4 + v)) =
-            make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-      if (kSplitP) {
-#pragma unroll
-        for (int v = 0; v < 4; ++v)
-          *reinterpret_cast<uint4*>(sP + kOperandB + swz(row, half * 8 + c * 4 + v)) =
-              make_uint4(packed_lo[4 * v], packed_lo[4 * v + 1], packed_lo[4 * v + 2], packed_lo[4 * v + 3]);
-      }
-    }
-    // ---- rescale O where a running maximum moved (the previous O += P V has completed) ----
-    if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        tmem_ld32(tO + lane_addr + c * 32, r);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-        tmem_st32(tO + lane_addr + c * 32, r);
-      }
-    }
-    fence_async_proxy();
-    tc_fence_before();
-    __syncthreads();  // P complete, S fully read, O rescaled
-    if (tid == 0) {
-      tc_fence_after();
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        // A = P: keys 16k.. of every row (K-major); B = V: key rows 16k.. , d along MN
-        const uint64_t a = smem_desc(sP + (k >> 2) * kChunkB + (k & 3) * 32, 0, 1024);
-        const uint64_t b = smem_desc(sV + buf * kOperandB + k * (16 * 128), kChunkB, 1024);
-        umma_f16(tO, a, b, kIdescPV, (j > 0 || k > 0) ? 1u : 0u);
-      }
-      if (kSplitP) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint64_t a = smem_desc(sP + kOperandB + (k >> 2) * kChunkB + (k & 3) * 32, 0, 1024);
-          const uint64_t b = smem_desc(sV + buf * kOperandB + k * (16 * 128), kChunkB, 1024);
-          umma_f16(tO, a, b, kIdescPV, 1u);
-        }
-      }
-      umma_commit(bar_o);
-    }
-    failed = !mbar_wait_bounded(bar_o, j & 1);
-    if (__syncthreads_or(failed)) { failed = true; break; }
-    tc_fence_after();
+    if (!failed && nA == nB && nA > 0 && wait_all(o_full, 0))
+      write_item<T>(tmem + 256, lane_addr, row, half, pd.it[0], p.num_q_heads, p.out, s_half, st[0]);
+    if (!failed && wait_all(o_full + 1, 0))
+      write_item<T>(tmem + 384, lane_addr, row, half, pd.it[1], p.num_q_heads, p.out, s_half, st[1]);
   }
 
-  if (!failed) {
-    // ---- epilogue: out = O / l ----
-    // the row sum is the sum of the two column halves
-    s_half[half * kTile + row] = l_run;
-    __syncthreads();
-    const float l_row = l_run + s_half[(half ^ 1) * kTile + row];
-    const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-    uint8_t* orow = static_cast<uint8_t*>(p.out) + (int64_t(td.row0 + row) * p.num_q_heads + head) * (kD * 2) +
-                    half * 128;
-    uint32_t r[32];
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      tmem_ld32(tO + lane_addr + c * 32, r);
-      if (row < td.nrows) {
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint4 w;
-          w.x = pack2<T>(__uint_as_float(r[8 * v + 0]) * inv, __uint_as_float(r[8 * v + 1]) * inv);
-          w.y = pack2<T>(__uint_as_float(r[8 * v + 2]) * inv, __uint_as_float(r[8 * v + 3]) * inv);
-          w.z = pack2<T>(__uint_as_float(r[8 * v + 4]) * inv, __uint_as_float(r[8 * v + 5]) * inv);
-          w.w = pack2<T>(__uint_as_float(r[8 * v + 6]) * inv, __uint_as_float(r[8 * v + 7]) * inv);
-          *reinterpret_cast<uint4*>(orow + (c * 4 + v) * 16) = w;
-        }
-      }
-    }
-  } else if (tid == 0) {
-    atomicMax(p.status, KPX_ERR_DEVICE_TIMEOUT);
-  }
-  cp_async_wait_all();  // nothing of ours may still be landing in shared memory
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 256);
+  if (tid == 0 && *abort_flag) atomicMax(p.status, KPX_ERR_DEVICE_TIMEOUT);
+  if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
 }  // namespace
 
-// Host side: tile list -> workspace, launch.  Returns KPX_ERR_UNIMPLEMENTED when the layout
-// or dtype is outside this path so that the caller can fall back to the streaming path.
+namespace {
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library carries no link
+// dependency on the driver library.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &res) != cudaSuccess ||
+        res != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+// rank-n map of 16-bit elements, 128-byte swizzle; dims/box innermost first, strides in bytes
+// for dimensions 1..n-1
+bool make_map(CUtensorMap* map, int32_t dtype, const void* base, int rank, const cuuint64_t* dims,
+              const cuuint64_t* strides_b, const cuuint32_t* box) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint32_t ones[4] = {1, 1, 1, 1};
+  return fn(map, dtype == KPX_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+            cuuint32_t(rank), const_cast<void*>(base), dims, strides_b, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace
+
+// Host side: pair list -> workspace, tensor maps, launch.  Returns KPX_ERR_UNIMPLEMENTED when
+// the layout, dtype or scale is outside this path so that the caller can fall back to the
+// streaming path.
 int prefill_tc(void* out, const void* q, const void* k_pool, const void* v_pool, const kpx_kv_layout* layout,
                const int32_t* block_table, int32_t max_blocks_per_seq, const int32_t* cu_q_lens_host,
                const int32_t* start_pos_host, int32_t batch, int32_t num_q_heads, float scale, void* tile_area,
                int64_t tile_area_bytes, int32_t* status, cudaStream_t stream) {
-  if (layout->dtype == KPX_F32 || layout->head_size != kD || layout->block_size != kBS || !tile_contiguous(layout) ||
-      !block_table)
+  if (layout->dtype == KPX_F32 || layout->head_size != kD || layout->block_size != kBS || !block_table ||
+      !(scale > 0.f))  // the row maximum is taken before scaling
     return KPX_ERR_UNIMPLEMENTED;
-  std::vector<TileDesc> tiles;
+  // TMA: 16-byte aligned bases (strides are multiples of 16 bytes in every valid layout)
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool)) & 15)
+    return KPX_ERR_UNIMPLEMENTED;
+  const int kv_mul = num_q_heads / layout->num_kv_heads;
+  const int32_t total_q = cu_q_lens_host[batch];
+  // Items of one (sequence, KV head) in ascending position order, taken two at a time.
+  std::vector<PairDesc> pairs;
   for (int32_t b = 0; b < batch; ++b) {
     const int32_t n = cu_q_lens_host[b + 1] - cu_q_lens_host[b];
-    for (int32_t t0 = 0; t0 < n; t0 += kTile)
-      tiles.push_back(TileDesc{b, cu_q_lens_host[b] + t0, n - t0 < kTile ? n - t0 : kTile, start_pos_host[b] + t0});
+    if (n <= 0) continue;
+    for (int32_t kvh = 0; kvh < layout->num_kv_heads; ++kvh) {
+      PairDesc pd{b, kvh, {{0, 0, 0, 0}, {0, 0, 0, 0}}};
+      int held = 0;
+      for (int32_t t0 = 0; t0 < n; t0 += kTile)
+        for (int32_t h = kvh * kv_mul; h < (kvh + 1) * kv_mul; ++h) {
+          const ItemDesc it{cu_q_lens_host[b] + t0, n - t0 < kTile ? n - t0 : kTile, start_pos_host[b] + t0, h};
+          pd.it[held++] = it;
+          if (held == 2) {
+            pairs.push_back(pd);
+            held = 0;
+          }
+        }
+      if (held == 1) {  // a single item travels as it[1]
+        pd.it[1] = pd.it[0];
+        pd.it[0] = ItemDesc{0, 0, 0, 0};
+        pairs.push_back(pd);
+      }
+    }
   }
-  if (tiles.empty()) return KPX_OK;
-  if (int64_t(tiles.size() * sizeof(TileDesc)) > tile_area_bytes) return KPX_ERR_WORKSPACE_TOO_SMALL;
-  KPX_CUDA_TRY(cudaMemcpyAsync(tile_area, tiles.data(), tiles.size() * sizeof(TileDesc), cudaMemcpyHostToDevice, stream));
+  if (pairs.empty()) return KPX_OK;
+  // longest first: the hardware hands CTAs out in order, so the short ones fill the tail
+  auto cost = [](const PairDesc& d) {
+    auto tiles = [](const ItemDesc& it) { return it.nrows > 0 ? (it.pos0 + it.nrows - 1) / kTile + 1 : 0; };
+    return tiles(d.it[0]) + tiles(d.it[1]);
+  };
+  std::stable_sort(pairs.begin(), pairs.end(), [&](const PairDesc& a, const PairDesc& b) { return cost(a) > cost(b); });
+  if (int64_t(pairs.size() * sizeof(PairDesc)) > tile_area_bytes) return KPX_ERR_WORKSPACE_TOO_SMALL;
+
+  CUtensorMap map_q, map_k, map_v;
+  {
+    // Q [total_q][heads][128]: box = 128 rows x one head x 64 elements
+    const cuuint64_t dims[3] = {cuuint64_t(kD), cuuint64_t(num_q_heads), cuuint64_t(total_q)};
+    const cuuint64_t strides[2] = {cuuint64_t(kD) * 2, cuuint64_t(num_q_heads) * kD * 2};
+    const cuuint32_t box[3] = {64, 1, cuuint32_t(kTile)};
+    if (!make_map(&map_q, layout->dtype, q, 3, dims, strides, box)) return KPX_ERR_UNIMPLEMENTED;
+  }
+  {
+    // pool [blocks][kv heads][16 tokens][128] by its strides: box = one (block, head) tile x 64 elements
+    const cuuint64_t nblocks = layout->num_blocks > 0 ? cuuint64_t(layout->num_blocks) : (cuuint64_t(1) << 24);
+    const cuuint64_t dims[4] = {cuuint64_t(kD), cuuint64_t(kBS), cuuint64_t(layout->num_kv_heads), nblocks};
+    const cuuint64_t strides[3] = {cuuint64_t(layout->token_stride) * 2, cuuint64_t(layout->head_stride) * 2,
+                                   cuuint64_t(layout->block_stride) * 2};
+    const cuuint32_t box[4] = {64, cuuint32_t(kBS), 1, 1};
+    if (!make_map(&map_k, layout->dtype, k_pool, 4, dims, strides, box) ||
+        !make_map(&map_v, layout->dtype, v_pool, 4, dims, strides, box))
+      return KPX_ERR_UNIMPLEMENTED;
+  }
+  KPX_CUDA_TRY(cudaMemcpyAsync(tile_area, pairs.data(), pairs.size() * sizeof(PairDesc), cudaMemcpyHostToDevice, stream));
   PrefillParams p;
   p.out = out;
-  p.q = q;
-  p.k_pool = static_cast<const uint8_t*>(k_pool);
-  p.v_pool = static_cast<const uint8_t*>(v_pool);
   p.block_table = block_table;
-  p.tiles = static_cast<const TileDesc*>(tile_area);
+  p.pairs = static_cast<const PairDesc*>(tile_area);
   p.status = status;
-  p.block_stride_b = layout->block_stride * 2;
-  p.head_stride_b = layout->head_stride * 2;
   p.num_blocks = layout->num_blocks;
   p.max_blocks_per_seq = max_blocks_per_seq;
   p.num_q_heads = num_q_heads;
-  p.kv_mul = num_q_heads / layout->num_kv_heads;
+  p.kv_mul = kv_mul;
   p.qscale = scale * kLog2e;
-  const unsigned grid = unsigned(tiles.size()) * unsigned(num_q_heads);
-  if (layout->dtype == KPX_F16) {
-    static int done = -1;
-    int dev = 0;
-    KPX_CUDA_TRY(cudaGetDevice(&dev));
-    if (done != dev) {
-      KPX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-      done = dev;
-    }
-    prefill_tc_kernel<__half><<<grid, 256, kSmemBytes, stream>>>(p);
-  } else {
-    static int done = -1;
-    int dev = 0;
-    KPX_CUDA_TRY(cudaGetDevice(&dev));
-    if (done != dev) {
-      KPX_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-      done = dev;
-    }
-    prefill_tc_kernel<__nv_bfloat16><<<grid, 256, kSmemBytes, stream>>>(p);
-  }
-  return cuda_status(cudaGetLastError());
+  const unsigned grid = unsigned(pairs.size());
+  auto launch = [&](auto kernel) -> int {
+    // the attribute is per device; setting it again costs next to nothing beside the launch
+    KPX_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    kernel<<<grid, kThreads, kSmemBytes, stream>>>(p, map_q, map_k, map_v);
+    return cuda_status(cudaGetLastError());
+  };
+  if (layout->dtype == KPX_F16) return launch(prefill_tc_kernel<__half>);
+  return launch(prefill_tc_kernel<__nv_bfloat16>);
 }
 
 }  // namespace kpx
