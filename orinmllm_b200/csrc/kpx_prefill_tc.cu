@@ -96,13 +96,6 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t* r) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-      ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t* r) {
   asm volatile(
@@ -189,22 +182,23 @@ __device__ __forceinline__ float unpack_hi<__half>(uint32_t w) {
 // per SM whatever its shared-memory and register footprint, so the overlap of softmax and
 // tensor-core work has to happen inside the CTA: each CTA carries two items (A, B) and
 // alternates between them.
-constexpr int kMmaWarp = 8, kLoadWarp = 9;  // warps 0..7 run the softmax
-constexpr int kThreads = 320;
+constexpr int kMmaWarp = 16, kLoadWarp = 17;  // warps 0..7: softmax of item 0, warps 8..15: of item 1
+constexpr int kThreads = 576;
 constexpr int kSmemBytes = 1024 /*align slack*/ + 2 * kOperandB /*Q of A, B*/ + 2 * kOperandB /*K x2*/ +
                            2 * kOperandB /*V x2*/ + 256 /*barriers, tmem slot, abort flag*/ +
-                           2 * kTile * 4 /*exchange between the two column halves of a row*/;
+                           2 * 2 * kTile * 4 /*per item: exchange between the two column halves of a row*/;
 
-// Barrier among the 256 softmax threads only (hardware barrier 1; barrier 0 is __syncthreads).
-__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// Barrier among the 256 softmax threads of one item (hardware barrier `id` = 1 or 2; barrier 0
+// is __syncthreads).
+__device__ __forceinline__ void softmax_sync(int id) { asm volatile("bar.sync %0, 256;" ::"r"(id) : "memory"); }
 // The same with a vote: true when any of the 256 threads passes true.
-__device__ __forceinline__ bool softmax_sync_or(bool pred) {
+__device__ __forceinline__ bool softmax_sync_or(int id, bool pred) {
   uint32_t out;
   asm volatile(
-      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\t"
-      "bar.red.or.pred q, 1, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %2, 0;\n\t"
+      "bar.red.or.pred q, %1, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
       : "=r"(out)
-      : "r"(uint32_t(pred))
+      : "r"(id), "r"(uint32_t(pred))
       : "memory");
   return out != 0;
 }
@@ -249,6 +243,12 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t addr, uint32_t* r) {
       : "r"(addr)
       : "memory");
 }
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Largest of 32 scores; with kMasked, scores of keys e > limit (newer than the query) do not count.
@@ -266,29 +266,40 @@ __device__ __forceinline__ float max32(const uint32_t* r, int limit, float mx) {
   return mx;
 }
 
+__device__ __forceinline__ void tmem_st8(uint32_t addr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
 // Weights of 32 keys: p = exp2(s * qscale - m), written back over the 32 columns of S they came
-// from as P_hi (16 columns, two keys each) and P_lo = p - P_hi (16 columns); lsum += p.
+// from as P_hi (columns 0..15, two keys each) and P_lo = p - P_hi (columns 16..31); lsum += p.
+// Sixteen keys at a time to keep the live registers down.
 template <typename T, bool kMasked>
 __device__ __forceinline__ void weights32(uint32_t taddr, const uint32_t* r, float qscale, float neg_m, int limit,
                                           float2& lsum) {
-  uint32_t hi[16], lo[16];
   const float2 sc = make_float2(qscale, qscale), nm = make_float2(neg_m, neg_m), m1 = make_float2(-1.f, -1.f);
 #pragma unroll
-  for (int e = 0; e < 32; e += 2) {
-    const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), sc, nm);
-    float2 w = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-    if (kMasked) {
-      if (e > limit) w.x = 0.f;
-      if (e + 1 > limit) w.y = 0.f;
+  for (int h = 0; h < 2; ++h) {
+    uint32_t hi[8], lo[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int e = h * 16 + 2 * i;
+      const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), sc, nm);
+      float2 w = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+      if (kMasked) {
+        if (e > limit) w.x = 0.f;
+        if (e + 1 > limit) w.y = 0.f;
+      }
+      lsum = __fadd2_rn(lsum, w);
+      const uint32_t hw = pack2<T>(w.x, w.y);
+      hi[i] = hw;
+      const float2 d = __ffma2_rn(make_float2(unpack_lo<T>(hw), unpack_hi<T>(hw)), m1, w);
+      lo[i] = pack2<T>(d.x, d.y);
     }
-    lsum = __fadd2_rn(lsum, w);
-    const uint32_t h = pack2<T>(w.x, w.y);
-    hi[e >> 1] = h;
-    const float2 d = __ffma2_rn(make_float2(unpack_lo<T>(h), unpack_hi<T>(h)), m1, w);
-    lo[e >> 1] = pack2<T>(d.x, d.y);
+    tmem_st8(taddr + h * 8, hi);
+    tmem_st8(taddr + 16 + h * 8, lo);
   }
-  tmem_st16(taddr, hi);
-  tmem_st16(taddr + 16, lo);
 }
 
 // Per-thread softmax state of one item: this thread owns (row, column half) of S and O.
@@ -302,10 +313,12 @@ struct RowState {
 constexpr float kLazyMax = 8.f;
 
 // Softmax of tile j of one item: S (tensor memory, 128 columns at tS) -> P over S, O rescaled
-// where the row maximum moved.  Called by the 256 softmax threads (contains their barrier).
+// where the row maximum moved.  Called by the 256 softmax threads of the item (contains their
+// barrier `bar_id`).
 template <typename T>
 __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t lane_addr, int row, int half,
-                                             float qscale, int j, int pos0, float* s_half, RowState& st) {
+                                             float qscale, int j, int pos0, float* s_half, int bar_id,
+                                             RowState& st) {
   const int my_pos = pos0 + row;
   const bool diag = (j * kTile + kTile - 1) > pos0;  // some row of this item is masked in this tile
   const int limit0 = my_pos - (j * kTile + half * 64);   // keys e > limit are newer than the query
@@ -317,7 +330,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t 
   if (diag) mx = max32<true>(r1, limit0 - 32, max32<true>(r0, limit0, -INFINITY));
   else mx = max32<false>(r1, 0, max32<false>(r0, 0, -INFINITY));
   s_half[half * kTile + row] = mx;
-  softmax_sync();  // the other half of the row has published its maximum
+  softmax_sync(bar_id);  // the other half of the row has published its maximum
   const float m_tile = fmaxf(mx, s_half[(half ^ 1) * kTile + row]) * qscale;
   float alpha = 1.f;
   if (m_tile > st.m + kLazyMax || st.m == -INFINITY) {  // (-inf + 8 is -inf: the first tile always moves it)
@@ -348,14 +361,14 @@ __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t 
   tmem_wait_st();
 }
 
-// out rows of one item = O / l.  Called by the 256 softmax threads (contains their barrier).
+// out rows of one item = O / l.  Called by the 256 softmax threads of the item (contains their barrier).
 template <typename T>
 __device__ __forceinline__ void write_item(uint32_t tO, uint32_t lane_addr, int row, int half, const ItemDesc& it,
-                                           int num_q_heads, void* out, float* s_half, const RowState& st) {
+                                           int num_q_heads, void* out, float* s_half, int bar_id, const RowState& st) {
   const float l_mine = st.l.x + st.l.y;
-  softmax_sync();  // earlier readers of the exchange area are done
+  softmax_sync(bar_id);  // earlier readers of the exchange area are done
   s_half[half * kTile + row] = l_mine;
-  softmax_sync();
+  softmax_sync(bar_id);
   const float l_row = l_mine + s_half[(half ^ 1) * kTile + row];
   const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
   uint8_t* orow = static_cast<uint8_t*>(out) + (int64_t(it.row0 + row) * num_q_heads + it.head) * (kD * 2) + half * 128;
@@ -398,7 +411,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* tail_ok = bars + 15;   // rows past the newest token are zero in the last V tile
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
-  float* s_half = reinterpret_cast<float*>(sV + 2 * kOperandB + 256);  // [2][128]
+  float* s_half = reinterpret_cast<float*>(sV + 2 * kOperandB + 256);  // [2 items][2][128]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const PairDesc pd = p.pairs[blockIdx.x];
@@ -477,113 +490,126 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else if (warp == kMmaWarp) {
-    // ===== MMA issue: one thread =====
-    if (lane == 0) {
-      constexpr uint32_t kIdescQK = instr_desc(Fmt<T>::kCode, Fmt<T>::kCode, 0);
-      constexpr uint32_t kIdescPV = instr_desc(Fmt<T>::kCode, Fmt<T>::kCode, 1);
-      // descriptors of the operand bases; the k steps add to the 16-byte-unit address field
-      const uint64_t dq[2] = {smem_desc(sQ, 0, 1024), smem_desc(sQ + kOperandB, 0, 1024)};
-      const uint64_t dk[2] = {smem_desc(sK, 0, 1024), smem_desc(sK + kOperandB, 0, 1024)};
-      const uint64_t dv[2] = {smem_desc(sV, kChunkB, 1024), smem_desc(sV + kOperandB, kChunkB, 1024)};
-      bool ok = true;
-      // S_x = Q_x K(j)^T: 8 steps of k = 16 over d = 128 (4 steps per 64-element slab)
-      auto issue_qk = [&](int x, int j) {
+    // ===== MMA issue.  The whole warp walks the schedule in step (every wait result is made
+    // warp-uniform) and one elected lane issues, so that descriptors and addresses stay in
+    // uniform registers =====
+    constexpr uint32_t kIdescQK = instr_desc(Fmt<T>::kCode, Fmt<T>::kCode, 0);
+    constexpr uint32_t kIdescPV = instr_desc(Fmt<T>::kCode, Fmt<T>::kCode, 1);
+    const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+    // descriptors of the operand bases; the k steps add to the 16-byte-unit address field
+    const uint64_t dq0 = smem_desc(sQ, 0, 1024), dk0 = smem_desc(sK, 0, 1024), dv0 = smem_desc(sV, kChunkB, 1024);
+    constexpr uint64_t kNextOperand = uint64_t(kOperandB >> 4);  // second item's Q, second stage of K / V
+    bool ok = true;
+    // S_x = Q_x K(j)^T: 8 steps of k = 16 over d = 128 (4 steps per 64-element slab)
+    auto issue_qk = [&](int x, int j) {
+      const uint64_t a = dq0 + uint64_t(x) * kNextOperand, b = dk0 + uint64_t(j & 1) * kNextOperand;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
-          const uint64_t o = uint64_t(((s >> 2) * kChunkB + (s & 3) * 32) >> 4);
-          umma_f16(tmem + x * 128, dq[x] + o, dk[j & 1] + o, kIdescQK, s > 0);
-        }
-        umma_commit(s_full + x);
-      };
-      // O_x += P_hi V(j) + P_lo V(j).  A = P from tensor memory: keys 16s.. of every row sit in 8
-      // columns; B = V: key rows 16s.., d along MN.  A and B of one MMA must have the same
-      // 16-bit format (an fp16 P against a bf16 V is an illegal instruction).  A single 16-bit P
-      // (2^-9 rounding for bf16, 2^-12 for fp16) costs up to a few 1e-3 absolute on short
-      // sequences, beyond the 2e-3 / 1e-2 output tolerance, hence the two terms.
-      auto issue_pv = [&](int x, int j) {
-        const uint32_t tP = tmem + x * 128, tO = tmem + 256 + x * 128;
+      for (int s = 0; s < 8; ++s) {
+        const uint64_t o = uint64_t(((s >> 2) * kChunkB + (s & 3) * 32) >> 4);
+        umma_f16(tm + x * 128, a + o, b + o, kIdescQK, s > 0);
+      }
+      umma_commit(s_full + x);
+    };
+    // O_x += P_hi V(j) + P_lo V(j).  A = P from tensor memory: keys 16s.. of every row sit in 8
+    // columns; B = V: key rows 16s.., d along MN.  A and B of one MMA must have the same 16-bit
+    // format (an fp16 P against a bf16 V is an illegal instruction).  A single 16-bit P (2^-9
+    // rounding for bf16, 2^-12 for fp16) costs up to a few 1e-3 absolute on short sequences,
+    // beyond the 2e-3 / 1e-2 output tolerance, hence the two terms.
+    auto issue_pv = [&](int x, int j) {
+      const uint32_t tP = tm + x * 128, tO = tm + 256 + x * 128;
+      const uint64_t b = dv0 + uint64_t(j & 1) * kNextOperand;
 #pragma unroll
-        for (int s = 0; s < 8; ++s)
-          umma_f16_ts(tO, tP + (s >> 1) * 32 + (s & 1) * 8, dv[j & 1] + uint64_t((s * 16 * 128) >> 4), kIdescPV,
-                      (j > 0 || s > 0) ? 1u : 0u);
+      for (int s = 0; s < 8; ++s)
+        umma_f16_ts(tO, tP + (s >> 1) * 32 + (s & 1) * 8, b + uint64_t((s * 16 * 128) >> 4), kIdescPV,
+                    (j > 0 || s > 0) ? 1u : 0u);
 #pragma unroll
-        for (int s = 0; s < 8; ++s)
-          umma_f16_ts(tO, tP + (s >> 1) * 32 + 16 + (s & 1) * 8, dv[j & 1] + uint64_t((s * 16 * 128) >> 4), kIdescPV, 1u);
-      };
-      auto wait = [&](uint64_t* bar, int parity) {
-        ok = ok && wait_or_abort(bar, uint32_t(parity), abort_flag);
-        tc_fence_after();
-        return ok;
-      };
-      // K(j) / V(j) of stage j&1 are in their (j>>1)-th use; the last tile also waits for the zeroed tail
-      auto wait_k = [&](int j) { return wait(k_full + (j & 1), (j >> 1) & 1); };
-      auto wait_v = [&](int j) {
-        if (ragged && j == nB - 1 && !wait(tail_ok, 0)) return false;
-        return wait(v_full + (j & 1), (j >> 1) & 1);
-      };
-      if (wait(q_full, 0) && wait_k(0)) {
+      for (int s = 0; s < 8; ++s)
+        umma_f16_ts(tO, tP + (s >> 1) * 32 + 16 + (s & 1) * 8, b + uint64_t((s * 16 * 128) >> 4), kIdescPV, 1u);
+    };
+    auto wait = [&](uint64_t* bar, int parity) {
+      ok = ok && __all_sync(0xffffffffu, wait_or_abort(bar, uint32_t(parity), abort_flag));
+      tc_fence_after();
+      return ok;
+    };
+    // K(j) / V(j) of stage j&1 are in their (j>>1)-th use; the last tile also waits for the zeroed tail
+    auto wait_k = [&](int j) { return wait(k_full + (j & 1), (j >> 1) & 1); };
+    auto wait_v = [&](int j) {
+      if (ragged && j == nB - 1 && !wait(tail_ok, 0)) return false;
+      return wait(v_full + (j & 1), (j >> 1) & 1);
+    };
+    if (wait(q_full, 0) && wait_k(0)) {
+      if (elect_one()) {
         if (nA > 0) issue_qk(0, 0);
         issue_qk(1, 0);
         umma_commit(k_free);
       }
-      for (int j = 0; j < nB && ok; ++j) {
-        // item 0, while the softmax threads are busy with item 1 (and the other way round below)
-        if (j < nA) {
-          if (!wait(p_full, j & 1) || !wait_v(j)) break;
+      __syncwarp();
+    }
+    for (int j = 0; j < nB && ok; ++j) {
+      // item 0, while the softmax threads are busy with item 1 (and the other way round below)
+      if (j < nA) {
+        if (!wait(p_full, j & 1) || !wait_v(j)) break;
+        if (elect_one()) {
           issue_pv(0, j);
           if (j + 1 == nA) umma_commit(o_full);
         }
-        if (j + 1 < nA) {
-          if (!wait_k(j + 1)) break;
+        __syncwarp();
+      }
+      if (j + 1 < nA) {
+        if (!wait_k(j + 1)) break;
+        if (elect_one()) {
           issue_qk(0, j + 1);
         }
-        if (!wait(p_full + 1, j & 1) || !wait_v(j)) break;
+        __syncwarp();
+      }
+      if (!wait(p_full + 1, j & 1) || !wait_v(j)) break;
+      if (elect_one()) {
         issue_pv(1, j);
         umma_commit(v_free + (j & 1));
-        if (j + 1 == nB) {
-          umma_commit(o_full + 1);
-        } else {
-          if (!wait_k(j + 1)) break;
+        if (j + 1 == nB) umma_commit(o_full + 1);
+      }
+      __syncwarp();
+      if (j + 1 < nB) {
+        if (!wait_k(j + 1)) break;
+        if (elect_one()) {
           issue_qk(1, j + 1);
           umma_commit(k_free + ((j + 1) & 1));
         }
+        __syncwarp();
       }
     }
   } else {
-    // ===== softmax: 8 warps; warp w and warp w+4 share TMEM lanes (= query rows) 32*(w&3)..+31,
-    // the first owns columns 0..63 of S and O, the second columns 64..127 =====
-    const int row = tid & 127, half = tid >> 7;
-    const uint32_t lane_addr = (uint32_t((warp & 3) * 32) << 16) + uint32_t(half * 64);
-    RowState st[2];
-    bool failed = false;
-    auto wait_all = [&](uint64_t* bar, int parity) {
-      const bool bad = !wait_or_abort(bar, uint32_t(parity), abort_flag);
-      if (softmax_sync_or(bad)) failed = true;
-      tc_fence_after();
-      return !failed;
-    };
-    auto publish_p = [&](int x) {  // this warp's part of P_x is in tensor memory
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full + x);
-    };
-    for (int j = 0; j < nB; ++j) {
-      if (j < nA) {
-        if (!wait_all(s_full, j & 1)) break;
-        softmax_tile<T>(tmem, tmem + 256, lane_addr, row, half, p.qscale, j, pd.it[0].pos0, s_half, st[0]);
-        publish_p(0);
-      } else if (j == nA && nA > 0) {
-        if (!wait_all(o_full, 0)) break;
-        write_item<T>(tmem + 256, lane_addr, row, half, pd.it[0], p.num_q_heads, p.out, s_half, st[0]);
+    // ===== softmax: warps 0..7 own item 0, warps 8..15 item 1.  Within an item warp w and warp
+    // w+4 share TMEM lanes (= query rows) 32*(w&3)..+31; the first owns columns 0..63 of S and
+    // O, the second columns 64..127 =====
+    const int x = warp >> 3;                      // item
+    const int n_mine = x ? nB : nA;
+    if (n_mine > 0) {
+      const int t = tid & 255, row = t & 127, half = t >> 7;
+      const uint32_t lane_addr = (uint32_t((warp & 3) * 32) << 16) + uint32_t(half * 64);
+      const uint32_t tS = tmem + x * 128, tO = tmem + 256 + x * 128;
+      const ItemDesc it = pd.it[x];
+      float* my_half = s_half + x * 2 * kTile;
+      const int bar_id = 1 + x;
+      RowState st;
+      bool failed = false;
+      auto wait_all = [&](uint64_t* bar, int parity) {
+        const bool bad = !wait_or_abort(bar, uint32_t(parity), abort_flag);
+        if (softmax_sync_or(bar_id, bad)) failed = true;
+        tc_fence_after();
+        return !failed;
+      };
+      for (int j = 0; j < n_mine; ++j) {
+        if (!wait_all(s_full + x, j & 1)) break;
+        softmax_tile<T>(tS, tO, lane_addr, row, half, p.qscale, j, it.pos0, my_half, bar_id, st);
+        // this warp's part of P is in tensor memory
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full + x);
       }
-      if (!wait_all(s_full + 1, j & 1)) break;
-      softmax_tile<T>(tmem + 128, tmem + 384, lane_addr, row, half, p.qscale, j, pd.it[1].pos0, s_half, st[1]);
-      publish_p(1);
+      if (!failed && wait_all(o_full + x, 0))
+        write_item<T>(tO, lane_addr, row, half, it, p.num_q_heads, p.out, my_half, bar_id, st);
     }
-    if (!failed && nA == nB && nA > 0 && wait_all(o_full, 0))
-      write_item<T>(tmem + 256, lane_addr, row, half, pd.it[0], p.num_q_heads, p.out, s_half, st[0]);
-    if (!failed && wait_all(o_full + 1, 0))
-      write_item<T>(tmem + 384, lane_addr, row, half, pd.it[1], p.num_q_heads, p.out, s_half, st[1]);
   }
 
   tc_fence_before();
@@ -704,14 +730,20 @@ int prefill_tc(void* out, const void* q, const void* k_pool, const void* v_pool,
   p.kv_mul = kv_mul;
   p.qscale = scale * kLog2e;
   const unsigned grid = unsigned(pairs.size());
-  auto launch = [&](auto kernel) -> int {
-    // the attribute is per device; setting it again costs next to nothing beside the launch
-    KPX_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  auto launch = [&](auto kernel, uint64_t* done_mask) -> int {
+    // the shared-memory attribute is per device: set once per device (bit mask of devices 0..63)
+    int dev = 0;
+    KPX_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 64 || !((*done_mask >> dev) & 1)) {
+      KPX_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+      if (dev < 64) *done_mask |= uint64_t(1) << dev;
+    }
     kernel<<<grid, kThreads, kSmemBytes, stream>>>(p, map_q, map_k, map_v);
     return cuda_status(cudaGetLastError());
   };
-  if (layout->dtype == KPX_F16) return launch(prefill_tc_kernel<__half>);
-  return launch(prefill_tc_kernel<__nv_bfloat16>);
+  static uint64_t done_f16 = 0, done_bf16 = 0;  // racing first calls at worst set the attribute twice
+  if (layout->dtype == KPX_F16) return launch(prefill_tc_kernel<__half>, &done_f16);
+  return launch(prefill_tc_kernel<__nv_bfloat16>, &done_bf16);
 }
 
 }  // namespace kpx

@@ -1,7 +1,7 @@
 """BASELINE configs[2] (chunked prefill at the Qwen2.5-7B attention shape: 28 Q / 4 KV heads,
 d=128, bf16, 4 sequences of 2048 tokens in 512-token chunks, block 16, seeded random block
-placement) on random data: times every chunk call with CUDA events and prints TFLOP/s on the
-causal-exact FLOP count.  Also the small case the ncu capture under profiles/ was taken on.
+placement) on random data: times every chunk call with CUDA events (alone and synchronised, then
+queued back to back for the device time) and prints TFLOP/s on the causal-exact FLOP count.  Also the small case the ncu capture under profiles/ was taken on.
 
     python tests/profiling/prefill_case.py [reps] [path]      path: 0 tensor-core tiles, 1 streaming
 """
@@ -33,21 +33,43 @@ cu = (np.arange(B + 1) * CHUNK).astype(np.int32)
 nbytes = capi.prefill_workspace_bytes(B * CHUNK, H, HKV, D)
 ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
 capi.workspace_init(ws, nbytes)
-total_ms, total_flop = 0.0, 0.0
+NCH = PROMPT // CHUNK
+flops = [B * 4.0 * H * D * sum(c * CHUNK + i + 1 for i in range(CHUNK)) for c in range(NCH)]
+starts = [np.full(B, c * CHUNK, np.int32) for c in range(NCH)]
+
+
+def call(c):
+    capi.paged_prefill(out, q, kp, vp, lay, bt, table.shape[1], cu, starts[c], B, H, 1 / np.sqrt(D), ws, nbytes)
+
+
+# (1) one call at a time, synchronised: what a caller that waits for each chunk sees (host
+#     work of the call included)
 for rep in range(reps):
-    for c in range(PROMPT // CHUNK):
-        sp = np.full(B, c * CHUNK, np.int32)
+    for c in range(NCH):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        capi.paged_prefill(out, q, kp, vp, lay, bt, table.shape[1], cu, sp, B, H, 1 / np.sqrt(D), ws, nbytes)
+        call(c)
         e1.record()
         torch.cuda.synchronize()
-        flop = B * 4.0 * H * D * sum(c * CHUNK + i + 1 for i in range(CHUNK))
-        ms = e0.elapsed_time(e1)
         if rep == reps - 1:
-            print(f"chunk {c}: {ms * 1e3:8.1f} us  {flop / ms / 1e9:8.1f} TFLOP/s (causal-exact)")
-        if rep > 0 or reps == 1:
-            total_ms += ms
-            total_flop += flop
+            ms = e0.elapsed_time(e1)
+            print(f"chunk {c} alone : {ms * 1e3:8.1f} us  {flops[c] / ms / 1e9:8.1f} TFLOP/s (causal-exact)")
+# (2) device time: each chunk's call queued `queued` times back to back behind a long-running
+#     filler so that the host is ahead of the device; events bracket the queued calls
+queued = 20
+filler = torch.empty(1 << 28, dtype=torch.float32, device="cuda")
+total_ms = 0.0
+for c in range(NCH):
+    for _ in range(3):
+        filler.add_(1.0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(queued):
+        call(c)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / queued
+    total_ms += ms
+    print(f"chunk {c} queued: {ms * 1e3:8.1f} us  {flops[c] / ms / 1e9:8.1f} TFLOP/s (causal-exact)")
 print("status", capi.workspace_status(ws))
-print(f"all chunks: {total_flop / total_ms / 1e9:.1f} TFLOP/s, {total_ms / max(1, reps - 1) * 1e3:.1f} us per 4x2048-token prefill layer")
+print(f"all chunks (device time): {sum(flops) / total_ms / 1e9:.1f} TFLOP/s, {total_ms * 1e3:.1f} us per 4x2048-token prefill layer")
