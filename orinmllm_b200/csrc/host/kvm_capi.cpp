@@ -10,10 +10,7 @@
 #include "base/prefix_cache.h"
 #include "kpx_kvm.h"
 
-struct kpx_kvm {
-  std::unique_ptr<base::PagedKVManager> pool;
-  std::unique_ptr<base::PrefixCache> cache;
-};
+#include "kvm_handle.h"
 
 namespace {
 int to_code(const base::Status& s) { return s.get_err_code(); }

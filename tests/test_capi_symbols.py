@@ -53,3 +53,23 @@ def test_host_manager_library_exports_every_declared_symbol(native_libs):
     handle = ctypes.CDLL(str(so))
     assert not [s for s in declared if not hasattr(handle, s)]
     assert sorted(kvm.SIGNATURES) == declared
+
+
+def test_scheduler_header_symbols_exported(native_libs):
+    from orinmllm_b200 import build, sched
+    so = build.build_host()
+    text = (ROOT / "include" / "kpx_sched.h").read_text()
+    declared = sorted(set(re.findall(r"KPX_API\s+[\w\s\*]+?\b(kpx_sched_\w+)\s*\(", text)))
+    assert len(declared) >= 15
+    handle = ctypes.CDLL(str(so))
+    assert not [s for s in declared if not hasattr(handle, s)]
+    assert sorted(sched.SIGNATURES) == declared
+
+
+def test_scheduler_handles_reject_bad_arguments(native_libs):
+    from orinmllm_b200 import sched
+    lib = sched.lib()
+    assert not lib.kpx_sched_create(None, 512, 2048, 64, 256, 1)
+    assert lib.kpx_sched_submit(None, None, 0, 1, 0) == -1
+    assert lib.kpx_sched_admit(None) == -1
+    assert lib.kpx_sched_next_prefill(None) == 0 and lib.kpx_sched_next_decode(None) == 0

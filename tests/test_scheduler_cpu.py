@@ -1,0 +1,156 @@
+"""Host-side request scheduler (base::KVScheduler through include/kpx_sched.h): admission by free
+blocks, prefix reuse with copy-on-write, and the work lists handed to the kernels.  No GPU."""
+import numpy as np
+import pytest
+
+from orinmllm_b200 import kvm, sched
+
+BS = 16
+
+
+def drive(s, sample=lambda rid, step: 7, prefill_hook=None, decode_hook=None, max_steps=100000):
+    """Run the scheduler dry (no device): admit, prefill steps, decode steps, until idle."""
+    steps = 0
+    while s.num_waiting or s.num_running:
+        s.admit()
+        progressed = False
+        while True:
+            p = s.next_prefill()
+            if p is None:
+                break
+            progressed = True
+            if prefill_hook:
+                prefill_hook(p)
+            s.complete_prefill([sample(int(r), steps) for r in p.request_ids])
+        d = s.next_decode()
+        if d is not None:
+            progressed = True
+            if decode_hook:
+                decode_hook(d)
+            s.complete_decode([sample(int(r), steps) for r in d.request_ids])
+        steps += 1
+        assert progressed, "scheduler made no progress with requests outstanding"
+        assert steps < max_steps
+    return steps
+
+
+def check_slots(step_positions, slot_mapping, table_row):
+    for pos, slot in zip(step_positions, slot_mapping):
+        assert slot == int(table_row[pos // BS]) * BS + pos % BS
+
+
+def test_work_lists_are_consistent_and_chunked():
+    m = kvm.KvManager(512, BS, seed=3)
+    s = sched.Scheduler(m, prefill_chunk=48, max_prefill_tokens=100, max_prefill_rows=8, use_prefix_cache=False)
+    rng = np.random.default_rng(0)
+    prompts = {s.submit(rng.integers(0, 1000, n), 5): n for n in (130, 20, 75)}
+    seen = {rid: 0 for rid in prompts}
+
+    def on_prefill(p):
+        assert p.positions.size <= 100 and len(p.request_ids) <= 8
+        assert p.cu_q_lens[0] == 0 and p.cu_q_lens[-1] == p.positions.size
+        for i, rid in enumerate(p.request_ids):
+            a, b = p.cu_q_lens[i], p.cu_q_lens[i + 1]
+            assert 0 < b - a <= 48
+            assert p.start_pos[i] == seen[int(rid)]
+            assert list(p.positions[a:b]) == list(range(seen[int(rid)], seen[int(rid)] + b - a))
+            check_slots(p.positions[a:b], p.slot_mapping[a:b], p.block_table[i])
+            seen[int(rid)] += b - a
+            assert p.completes[i] == (seen[int(rid)] == prompts[int(rid)])
+
+    def on_decode(d):
+        for i, rid in enumerate(d.request_ids):
+            assert d.positions[i] == seen[int(rid)]
+            assert d.seq_lens[i] == seen[int(rid)] + 1
+            check_slots(d.positions[i:i + 1], d.slot_mapping[i:i + 1], d.block_table[i])
+            seen[int(rid)] += 1
+
+    drive(s, prefill_hook=on_prefill, decode_hook=on_decode)
+    st = s.stats()
+    assert st["finished"] == 3 and st["prefilled_tokens"] == 225 and st["decoded_tokens"] == 3 * 4
+    for rid, n in prompts.items():
+        assert s.state(rid) == 3 and len(s.tokens(rid)) == n + 5
+    assert m.num_free == 512  # no prefix cache: everything came back
+
+
+@pytest.mark.parametrize("prefix,suffix", [(64, 24), (60, 28)])
+def test_prefix_reuse_and_copy_on_write(prefix, suffix):
+    m = kvm.KvManager(2048, BS, seed=1)
+    s = sched.Scheduler(m, prefill_chunk=32)
+    rng = np.random.default_rng(5)
+    common = rng.integers(0, 151936, prefix)
+    first = s.submit(np.concatenate([common, rng.integers(0, 151936, suffix)]), 1, also_register=prefix)
+    drive(s)
+    assert s.reused_tokens(first) == 0
+    others = [s.submit(np.concatenate([common, rng.integers(0, 151936, suffix)]), 9) for _ in range(12)]
+    drive(s)
+    for rid in others:
+        assert s.reused_tokens(rid) == prefix
+        assert s.state(rid) == 3
+    st = s.stats()
+    assert st["reused_tokens"] == 12 * prefix
+    assert st["prefilled_tokens"] == (prefix + suffix) + 12 * suffix
+    # an unaligned prefix ends in a shared, partly filled block: every follower copies it once
+    assert m.cow_events == (12 if prefix % BS else 0)
+    ps = m.prefix_stats()
+    assert ps["cache_hits"] == 12
+
+
+def test_full_hit_recomputes_the_last_prompt_token():
+    m = kvm.KvManager(256, BS, seed=2)
+    s = sched.Scheduler(m)
+    prompt = np.arange(100, 150, dtype=np.int32)
+    a = s.submit(prompt, 1)
+    drive(s)
+    b = s.submit(prompt, 3)
+    drive(s)
+    assert s.reused_tokens(a) == 0 and s.reused_tokens(b) == len(prompt) - 1
+    assert s.stats()["prefilled_tokens"] == len(prompt) + 1
+
+
+def test_admission_waves_never_exhaust_the_pool():
+    nblocks = 200
+    m = kvm.KvManager(nblocks, BS, seed=9)
+    s = sched.Scheduler(m, prefill_chunk=64, max_prefill_tokens=256, use_prefix_cache=False)
+    rng = np.random.default_rng(11)
+    want = {}
+    for _ in range(60):
+        n, g = int(rng.integers(20, 400)), int(rng.integers(1, 40))
+        want[s.submit(rng.integers(0, 1000, n), g)] = n + g
+    peak_running = 0
+
+    def watch(_):
+        nonlocal peak_running
+        peak_running = max(peak_running, s.num_running)
+        assert m.num_free >= 0
+
+    drive(s, prefill_hook=watch, decode_hook=watch)
+    st = s.stats()
+    assert st["finished"] == 60 and st["admission_stalls"] > 0
+    assert 0 < st["peak_blocks_in_use"] <= nblocks
+    assert peak_running < 60  # it really ran in waves
+    for rid, total in want.items():
+        assert len(s.tokens(rid)) == total
+    assert m.num_free == nblocks
+
+
+def test_shared_prompt_workload_block_count():
+    """256 requests = common 1024-id prefix + unique 256-id suffix, 128 decode steps each: the pool
+    holds 64 shared blocks plus 24 private blocks per request."""
+    n_req, prefix, suffix, gen = 256, 1024, 256, 129  # 129 sampled tokens = 128 cached decode positions
+    m = kvm.KvManager(8192, BS, seed=4)
+    s = sched.Scheduler(m, prefill_chunk=512, max_prefill_tokens=4096, max_decode_batch=256)
+    rng = np.random.default_rng(1)
+    common = rng.integers(0, 151936, prefix)
+    first = s.submit(np.concatenate([common, rng.integers(0, 151936, suffix)]), 1, also_register=prefix)
+    drive(s)
+    s.forget(first)
+    for _ in range(n_req - 1):
+        s.submit(np.concatenate([common, rng.integers(0, 151936, suffix)]), gen)
+    drive(s)
+    st = s.stats()
+    assert st["finished"] == n_req and st["reused_tokens"] == (n_req - 1) * prefix
+    per_request = (suffix + gen - 1 + BS - 1) // BS  # 24
+    # request 0 keeps its 16 suffix blocks in the tree; the 255 followers ran together
+    assert st["peak_blocks_in_use"] == prefix // BS + suffix // BS + (n_req - 1) * per_request
+    assert m.cow_events == 0
