@@ -56,6 +56,7 @@ class ServingSim:
         self.decode_launches = 0
         self.prefill_launches = 0
         self.steps = 0
+        self.decode_events = None   # set to a list to collect (start, stop, algorithmic bytes) per decode launch
 
     # ---- one step of each kind --------------------------------------------------------------
     def _flush(self):
@@ -106,8 +107,14 @@ class ServingSim:
             capi.rope_append(q, k, v, self.H, pos, self.sin, self.cos, self.kp[l], self.vp[l], self.layout, slots,
                              rows)
             out = torch.empty_like(q)
+            if self.decode_events is not None:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
             capi.paged_decode(out, q, self.kp[l], self.vp[l], self.layout, table, table.shape[1], lens, 0, rows,
                               self.H, self.scale, self.ws, self.ws_bytes)
+            if self.decode_events is not None:
+                e1.record()
+                self.decode_events.append((e0, e1, int(d.seq_lens.sum()) * self.HKV * self.D * self.kp.element_size() * 2))
             self.decode_launches += 1
             if self.record:
                 outs.append(out.float().cpu().numpy())
