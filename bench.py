@@ -158,19 +158,27 @@ class DecodeWorkload:
         self.p_sin, self.p_cos = self.sin.data_ptr(), self.cos.data_ptr()
         self.p_table, self.p_ws = self.table.data_ptr(), self.ws.data_ptr()
         self.stream = self.torch.cuda.current_stream().cuda_stream
+        # the step a CUDA graph works on: positions and slots of the current step, refreshed by
+        # two small device-to-device copies before each replay
+        self.cur_pos = self.torch.empty(BATCH, dtype=self.torch.int32, device=self.dev)
+        self.cur_slots = self.torch.empty(BATCH, dtype=self.torch.int64, device=self.dev)
+        self.graph_resident = self.graph_e2e = None
 
-    def layer(self, t, l, events=None):
+    def layer(self, t, l, events=None, stream=None):
+        """RoPE + append + attend of layer l.  t: step index into the precomputed positions and
+        slots, or None for the current-step buffers (graph capture)."""
         capi = self.capi
-        pos = self.p_pos + t * BATCH * 4
+        stream = self.stream if stream is None else stream
+        pos = self.cur_pos.data_ptr() if t is None else self.p_pos + t * BATCH * 4
+        slots = self.cur_slots.data_ptr() if t is None else self.p_slots + t * BATCH * 8
         capi.rope_append(self.p_q[l], self.p_k[l], self.p_v[l], Q_HEADS, pos, self.p_sin, self.p_cos,
-                         self.p_kpool[l], self.p_vpool[l], self.layout, self.p_slots + t * BATCH * 8,
-                         BATCH, stream=self.stream)
+                         self.p_kpool[l], self.p_vpool[l], self.layout, slots, BATCH, stream=stream)
         if events is not None:
             events[0].record()
         # tokens cached before the step + 1 appended = attended length (len_bias = 1)
         capi.paged_decode(self.p_out[l], self.p_q[l], self.p_kpool[l], self.p_vpool[l], self.layout,
                           self.p_table, self.max_blocks, pos, 1, BATCH, Q_HEADS, self.scale,
-                          self.p_ws, self.ws_bytes, stream=self.stream)
+                          self.p_ws, self.ws_bytes, stream=stream)
         if events is not None:
             events[1].record()
         self.launches += 2
@@ -191,6 +199,50 @@ class DecodeWorkload:
             self.v[l].copy_(self.h_v[l], non_blocking=True)
             self.layer(t, l)
             self.h_out[l].copy_(self.out[l], non_blocking=True)
+
+    # ---- the same steps as CUDA graphs (captured once, replayed per step) ----
+    def _set_step(self, t):
+        self.cur_pos.copy_(self.positions[t], non_blocking=True)
+        self.cur_slots.copy_(self.slots[t], non_blocking=True)
+
+    def capture(self):
+        """Captures the resident step (72 kernels) and the end-to-end step (the same kernels with
+        every layer's host->device and device->host copies on side streams, so that copies of
+        one layer run under the kernels of its neighbours).  Capture executes nothing."""
+        torch = self.torch
+        main, h2d, d2h = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
+        count = self.launches
+        self.graph_resident = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph_resident, stream=main):
+            for l in range(LAYERS):
+                self.layer(None, l, stream=main.cuda_stream)
+        self.graph_e2e = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph_e2e, stream=main):
+            h2d.wait_stream(main)
+            d2h.wait_stream(main)
+            for l in range(LAYERS):
+                with torch.cuda.stream(h2d):
+                    self.q[l].copy_(self.h_q[l], non_blocking=True)
+                    self.k[l].copy_(self.h_k[l], non_blocking=True)
+                    self.v[l].copy_(self.h_v[l], non_blocking=True)
+                main.wait_stream(h2d)
+                self.layer(None, l, stream=main.cuda_stream)
+                d2h.wait_stream(main)
+                with torch.cuda.stream(d2h):
+                    self.h_out[l].copy_(self.out[l], non_blocking=True)
+            main.wait_stream(h2d)
+            main.wait_stream(d2h)
+        self.launches = count  # capture launched nothing
+
+    def replay_resident(self, t):
+        self._set_step(t)
+        self.graph_resident.replay()
+        self.launches += 2 * LAYERS
+
+    def replay_e2e(self, t):
+        self._set_step(t)
+        self.graph_e2e.replay()
+        self.launches += 2 * LAYERS
 
     def kv_bytes_step(self, t):
         return kv_bytes_per_layer(self.lens0 + t + 1) * LAYERS
@@ -277,7 +329,8 @@ def run_gpu(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
     W, K = args.warmup, args.steps
-    total_steps = 2 * (W + K)
+    use_graph = not args.no_graph
+    total_steps = 2 * (W + K) + K + 2
     wl = DecodeWorkload(rank, total_steps, device)
 
     def barrier():
@@ -291,10 +344,17 @@ def run_gpu(args):
         return multigpu.max_over_ranks(ms, world, device)
 
     sampler = ClockSampler(local) if rank == 0 else None
-    # ---- device-resident phase ----
     t = 0
+    wl.step_resident(t)  # first-use work (attributes, module load) before any capture
+    t += 1
+    if use_graph:
+        torch.cuda.synchronize(device)
+        wl.capture()
+    resident = wl.replay_resident if use_graph else wl.step_resident
+    end_to_end = wl.replay_e2e if use_graph else wl.step_e2e
+    # ---- device-resident phase ----
     for _ in range(W):
-        wl.step_resident(t)
+        resident(t)
         t += 1
     barrier()
     if sampler:
@@ -305,23 +365,35 @@ def run_gpu(args):
     bytes_resident = 0
     e0.record()
     for _ in range(K):
-        wl.step_resident(t, pairs)
+        if use_graph:
+            resident(t)
+        else:
+            wl.step_resident(t, pairs)
         bytes_resident += wl.kv_bytes_step(t)
         t += 1
     e1.record()
     barrier()
     ms_resident = max_over_ranks(e0.elapsed_time(e1))
     launches = wl.launches
+    if use_graph:
+        # kernels inside a graph cannot be bracketed by events: the per-launch durations of the
+        # roofline come from the same K steps launched one by one right after the timed replays
+        for _ in range(K):
+            wl.step_resident(t, pairs)
+            t += 1
+        barrier()
     decode_ms = [a.elapsed_time(b) for a, b in pairs]
     # ---- end-to-end phase (host buffers) ----
+    wl.step_e2e(t)
+    t += 1
     for _ in range(W):
-        wl.step_e2e(t)
+        end_to_end(t)
         t += 1
     barrier()
     bytes_e2e = 0
     e0.record()
     for _ in range(K):
-        wl.step_e2e(t)
+        end_to_end(t)
         bytes_e2e += wl.kv_bytes_step(t)
         t += 1
     e1.record()
@@ -352,7 +424,9 @@ def run_gpu(args):
                                "fp16 KV, block 16, bs=64 per GPU, ctx U[128,4096], pool x1.25, "
                                "seeded random block table; step = RoPE+append+attend over 36 layers",
                    "layers": LAYERS, "batch_per_gpu": BATCH, "partition": "by request, no collective",
-                   "l2": "inputs larger than L2: every layer has its own 0.66 GB pool"},
+                   "l2": "inputs larger than L2: every layer has its own 0.66 GB pool",
+                   "launch": ("one CUDA graph replay per step (72 kernels; end to end: plus 108 H2D and 36 D2H "
+                              "copies on side streams)") if use_graph else "one launch per kernel"},
         "tokens_per_s": round(world * BATCH / (ms_resident / K / 1e3), 1),
         "pct_of_8TBs_per_gpu": round(100 * value / world / 8000.0, 2),
         "e2e": {"value": round(e2e, 1), "unit": "GB/s", "h2d_bytes_per_step": wl.h2d_bytes_per_step(),
@@ -362,6 +436,8 @@ def run_gpu(args):
         "roofline": {"bound": "hbm", "kernel": "paged_decode_kernel", "achieved": round(achieved, 1),
                      "peak": peak, "peak_source": peak_src, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "avg_launch_us": round(avg_decode_ms * 1e3, 2),
+                     "timed": ("CUDA events around each decode launch of K steps launched one by one right after "
+                               "the timed graph replays") if use_graph else "CUDA events inside the timed region",
                      "algorithmic_bytes_per_launch": int(per_launch_bytes),
                      "traffic": int(per_launch_bytes * TRAFFIC_RATIO), "traffic_note": TRAFFIC_NOTE},
         "cpu_baseline": {"value": round(cpu_gbs, 3), "unit": "GB/s", "cores": 1, "kind": "port",
@@ -386,6 +462,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel separately instead of replaying CUDA graphs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
     if args.impl == "reference":
