@@ -9,11 +9,15 @@ token of every sequence, append K/V into that layer's pool, then attend over the
 context through the block table.  Every layer has its own 0.66 GB pool, so consecutive
 launches never find their input in L2.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-graph]
 
 Prints ONE JSON line (rank 0).  `value` is KV-read GB/s (algorithmic bytes / device time,
 whole job); `e2e` is the same metric with the step's Q/K/V rows coming from pinned host
 memory and the attention output going back to the host inside the timed region.
+The step is captured once as a CUDA graph and replayed (the way the reference runs its decode
+step); `--no-graph` launches every kernel separately.  The roofline's per-launch duration is
+taken with CUDA events around every decode launch: inside the timed region with `--no-graph`,
+otherwise over the same K steps launched one by one right after the timed replays.
 `--impl reference` times the CPU restatement of the reference's fp32 MHA path (the oracle,
 all host threads) on a bounded sample of the same workload.
 """
