@@ -102,6 +102,21 @@ KPX_API int kpx_rope_append(void* q, void* k, const void* v, int32_t q_heads,
                             const kpx_kv_layout* layout, const int64_t* slot_mapping,
                             int32_t num_tokens, void* stream);
 
+/* kpx_rope_append with the per-head RMSNorm of Qwen3 in front of the rotation: every head row
+ * x of Q (weights q_norm_weight) and of K (k_norm_weight), both fp32 [head_size], becomes
+ * w * (x / sqrt(mean(x^2) + norm_eps)) in fp32 before it is rotated; the row is rounded to the
+ * cache dtype once, after the rotation.  A NULL weight pointer leaves that tensor unnormalised;
+ * with both NULL this is kpx_rope_append.
+ * Replaces the sequence RmsNorm(q) -> RmsNorm(k) -> RoPE -> cache store of the Qwen3 attention
+ * block (kuiper/source/model/qwen3.cpp:1019-1046,1090-1126; rmsnorm statement
+ * kuiper/source/op/kernels/cpu/rmsnorm_kernel.cpp:26-34, eps 1e-6 for Qwen). */
+KPX_API int kpx_norm_rope_append(void* q, void* k, const void* v, int32_t q_heads,
+                                 const float* q_norm_weight, const float* k_norm_weight, float norm_eps,
+                                 const int32_t* positions, int32_t pos_base, const float* sin_cache,
+                                 const float* cos_cache, void* k_pool, void* v_pool,
+                                 const kpx_kv_layout* layout, const int64_t* slot_mapping,
+                                 int32_t num_tokens, void* stream);
+
 /* fp32 sin/cos tables [max_seq_len, head_size]: table[pos*head_size + k] =
  * sin/cos(pos * theta^(-k/head_size)).  Replaces sin_cos_cache_calc_cu
  * (kuiper/source/op/kernels/cuda/rope_kernel.cuh:22-23). */

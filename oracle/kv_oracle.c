@@ -80,6 +80,23 @@ ORC_API void orc_rope_batched(int32_t start_pos, int32_t n, int32_t dim, int32_t
   }
 }
 
+/* Per-head RMSNorm of n rows of `heads` heads (Qwen3 q/k norm before RoPE), in place:
+ * kuiper/source/op/kernels/cpu/rmsnorm_kernel.cpp:26-34 applied to every head row
+ * (kuiper/source/model/qwen3.cpp:1019-1034 reshapes q / k to [heads, head_size] and
+ * calls it): mean = mean(x^2) + eps; out = w * ((1/sqrt(mean)) * x).  The mean is
+ * accumulated sequentially in fp32 (Armadillo's order is unspecified). */
+ORC_API void orc_rmsnorm_heads(float* x, int64_t rows, int32_t heads, int32_t head_size,
+                               const float* weight, float eps) {
+  for (int64_t r = 0; r < rows * heads; ++r) {
+    float* row = x + r * head_size;
+    float sum = 0.f;
+    for (int32_t i = 0; i < head_size; ++i) sum += row[i] * row[i];
+    const float mean = sum / (float)head_size + eps;
+    const float rs = 1.f / sqrtf(mean);
+    for (int32_t i = 0; i < head_size; ++i) row[i] = weight[i] * (rs * row[i]);
+  }
+}
+
 /* kuiper/source/op/kernels/cpu/softmax_kernel.cpp:4-15 */
 static void softmax_inplace(float* x, int32_t size) {
   float max_value = x[0];

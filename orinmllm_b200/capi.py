@@ -52,6 +52,7 @@ SIGNATURES = {
     "kpx_layout_contiguous": (C.c_int, [_LP, _I32, _I32, _I32, _I32]),
     "kpx_append": (C.c_int, [_P, _P, _LP, _P, _P, _P, _P, _I32, _I32, _P]),
     "kpx_rope_append": (C.c_int, [_P, _P, _P, _I32, _P, _I32, _P, _P, _P, _P, _LP, _P, _I32, _P]),
+    "kpx_norm_rope_append": (C.c_int, [_P, _P, _P, _I32, _P, _P, _F32, _P, _I32, _P, _P, _P, _P, _LP, _P, _I32, _P]),
     "kpx_sin_cos_cache": (C.c_int, [_P, _P, _I32, _I32, _F32, _P]),
     "kpx_decode_workspace_bytes": (_I64, [_I32, _I32, _I32, _I32]),
     "kpx_paged_decode": (C.c_int, [_P, _P, _P, _P, _LP, _P, _I32, _P, _I32, _I32, _I32, _F32,
@@ -155,6 +156,14 @@ def rope_append(q, k, v, q_heads, positions, sin_cache, cos_cache, k_pool, v_poo
     check(lib().kpx_rope_append(ptr(q), ptr(k), ptr(v), q_heads, ptr(positions), pos_base, ptr(sin_cache),
                                 ptr(cos_cache), ptr(k_pool), ptr(v_pool), C.byref(layout),
                                 ptr(slot_mapping), num_tokens, _stream(stream)), "kpx_rope_append")
+
+
+def norm_rope_append(q, k, v, q_heads, q_norm_weight, k_norm_weight, norm_eps, positions, sin_cache, cos_cache,
+                     k_pool, v_pool, layout, slot_mapping, num_tokens, stream=None, pos_base=0) -> None:
+    check(lib().kpx_norm_rope_append(ptr(q), ptr(k), ptr(v), q_heads, ptr(q_norm_weight), ptr(k_norm_weight),
+                                     norm_eps, ptr(positions), pos_base, ptr(sin_cache), ptr(cos_cache),
+                                     ptr(k_pool), ptr(v_pool), C.byref(layout), ptr(slot_mapping), num_tokens,
+                                     _stream(stream)), "kpx_norm_rope_append")
 
 
 def sin_cos_cache(sin_cache, cos_cache, head_size, max_seq_len, theta, stream=None) -> None:

@@ -69,7 +69,8 @@ __global__ void rope_append_kernel(T* __restrict__ q, T* __restrict__ k, const T
                                    const float* __restrict__ cos_cache, uint8_t* __restrict__ k_pool,
                                    uint8_t* __restrict__ v_pool,
                                    const int64_t* __restrict__ slot_mapping, int32_t num_tokens,
-                                   LayoutDev L) {
+                                   LayoutDev L, const float* __restrict__ q_norm_w,
+                                   const float* __restrict__ k_norm_w, float norm_eps) {
   constexpr int E = Elt<T>::kPer16B;
   const int hs = L.head_size;
   const int groups_per_head = hs / 2 / E;  // pair-groups per head
@@ -104,6 +105,24 @@ __global__ void rope_append_kernel(T* __restrict__ q, T* __restrict__ k, const T
     float lo[E], hi[E];
     Elt<T>::unpack(lo_raw, lo);
     Elt<T>::unpack(hi_raw, hi);
+    const float* norm_w = is_k ? k_norm_w : q_norm_w;
+    if (norm_w) {
+      // per-head RMSNorm before the rotation (Qwen3 q/k norm): the head's groups_per_head
+      // threads are consecutive lanes of one warp and walk this path together
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) ss = fmaf(hi[e], hi[e], fmaf(lo[e], lo[e], ss));
+      const int lane = threadIdx.x & 31;
+      const uint32_t head_mask = (groups_per_head >= 32 ? 0xffffffffu : ((1u << groups_per_head) - 1u))
+                                 << (lane & ~(groups_per_head - 1));
+      for (int m = 1; m < groups_per_head; m <<= 1) ss += __shfl_xor_sync(head_mask, ss, m);
+      const float rs = 1.f / sqrtf(ss / float(hs) + norm_eps);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        lo[e] = __ldg(norm_w + g * E + e) * (rs * lo[e]);
+        hi[e] = __ldg(norm_w + hs / 2 + g * E + e) * (rs * hi[e]);
+      }
+    }
     __align__(16) T lo_out[E];
     __align__(16) T hi_out[E];
 #pragma unroll
@@ -242,9 +261,12 @@ template <typename T>
 static int launch_rope(void* q, void* k, const void* v, int32_t q_heads, const int32_t* positions,
                        int32_t pos_base, const float* sin_cache, const float* cos_cache, void* k_pool, void* v_pool,
                        const LayoutDev& L, const int64_t* slot_mapping, int32_t num_tokens,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const float* q_norm_w = nullptr, const float* k_norm_w = nullptr,
+                       float norm_eps = 0.f) {
   constexpr int E = Elt<T>::kPer16B;
   int groups = L.head_size / 2 / E;
+  // the fused norm sums a head's squares across the `groups` consecutive lanes that hold it
+  if ((q_norm_w || k_norm_w) && (groups > 32 || (groups & (groups - 1)))) return KPX_ERR_UNIMPLEMENTED;
   int64_t work = int64_t(num_tokens) *
                  (((q ? q_heads : 0) + (k ? L.num_kv_heads : 0)) * groups +
                   ((v && v_pool) ? L.num_kv_heads * L.head_size / E : 0));
@@ -253,7 +275,7 @@ static int launch_rope(void* q, void* k, const void* v, int32_t q_heads, const i
   rope_append_kernel<T><<<grid_for(work, threads), threads, 0, stream>>>(
       static_cast<T*>(q), static_cast<T*>(k), static_cast<const T*>(v), q_heads, positions, pos_base,
       sin_cache, cos_cache, static_cast<uint8_t*>(k_pool), static_cast<uint8_t*>(v_pool),
-      slot_mapping, num_tokens, L);
+      slot_mapping, num_tokens, L, q_norm_w, k_norm_w, norm_eps);
   return cuda_status(cudaGetLastError());
 }
 
@@ -262,6 +284,16 @@ extern "C" int kpx_rope_append(void* q, void* k, const void* v, int32_t q_heads,
                                const float* cos_cache, void* k_pool, void* v_pool,
                                const kpx_kv_layout* layout, const int64_t* slot_mapping,
                                int32_t num_tokens, void* stream) {
+  return kpx_norm_rope_append(q, k, v, q_heads, nullptr, nullptr, 0.f, positions, pos_base, sin_cache, cos_cache,
+                              k_pool, v_pool, layout, slot_mapping, num_tokens, stream);
+}
+
+extern "C" int kpx_norm_rope_append(void* q, void* k, const void* v, int32_t q_heads, const float* q_norm_weight,
+                                    const float* k_norm_weight, float norm_eps, const int32_t* positions,
+                                    int32_t pos_base, const float* sin_cache, const float* cos_cache,
+                                    void* k_pool, void* v_pool, const kpx_kv_layout* layout,
+                                    const int64_t* slot_mapping, int32_t num_tokens, void* stream) {
+  if ((q_norm_weight || k_norm_weight) && !(norm_eps >= 0.f)) return KPX_ERR_INVALID_ARGUMENT;
   if (!layout_ok(layout) || !sin_cache || !cos_cache || num_tokens < 0)
     return KPX_ERR_INVALID_ARGUMENT;
   if (q && q_heads <= 0) return KPX_ERR_INVALID_ARGUMENT;
@@ -276,11 +308,14 @@ extern "C" int kpx_rope_append(void* q, void* k, const void* v, int32_t q_heads,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (layout->dtype) {
     case KPX_F16:
-      return launch_rope<__half>(q, k, v, q_heads, positions, pos_base, sin_cache, cos_cache, k_pool, v_pool, L, slot_mapping, num_tokens, s);
+      return launch_rope<__half>(q, k, v, q_heads, positions, pos_base, sin_cache, cos_cache, k_pool, v_pool, L, slot_mapping, num_tokens, s,
+                                 q_norm_weight, k_norm_weight, norm_eps);
     case KPX_BF16:
-      return launch_rope<__nv_bfloat16>(q, k, v, q_heads, positions, pos_base, sin_cache, cos_cache, k_pool, v_pool, L, slot_mapping, num_tokens, s);
+      return launch_rope<__nv_bfloat16>(q, k, v, q_heads, positions, pos_base, sin_cache, cos_cache, k_pool, v_pool, L, slot_mapping, num_tokens, s,
+                                 q_norm_weight, k_norm_weight, norm_eps);
     default:
-      return launch_rope<float>(q, k, v, q_heads, positions, pos_base, sin_cache, cos_cache, k_pool, v_pool, L, slot_mapping, num_tokens, s);
+      return launch_rope<float>(q, k, v, q_heads, positions, pos_base, sin_cache, cos_cache, k_pool, v_pool, L, slot_mapping, num_tokens, s,
+                                 q_norm_weight, k_norm_weight, norm_eps);
   }
 }
 

@@ -49,6 +49,7 @@ struct DecodeParams {
   int32_t max_blocks_per_seq, len_bias, batch;
   int32_t num_q_heads, num_kv_heads, kv_mul;
   int32_t head_groups;  // ceil(kv_mul / QH)
+  int32_t partial_slots;  // slots of kPartialFloats floats in `partials`
   int32_t tile_contig;
   float qscale;  // softmax scale * log2(e)
 };
@@ -413,54 +414,151 @@ paged_decode_kernel(const DecodeParams p) {
     // every warp between the owners of the item's first and last block holds a piece of it
     const int64_t c_first = split.owner(item_start), c_last = split.owner(item_start + item.nblk - 1);
     const int pieces = int(c_last - c_first) + 1;
-    int* cnt = p.counters + (item.b * (p.num_kv_heads * p.head_groups) + item.sub);
-    int prev = 0;
-    if (lane == 0)  // release our piece, acquire the others' (device scope, cumulative over the warp)
-      asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(prev) : "l"(cnt) : "memory");
-    prev = __shfl_sync(0xffffffffu, prev, 0);
-    if (prev != pieces - 1) return;
-    if (lane == 0) *cnt = 0;
-    __syncwarp();
-    // token group tg assembles the heads j with j % TG == tg; lane `sub` its DPT dims
-    for (int j = tg; j < QH; j += TG) {
-      const int hq = hg * QH + j;
-      if (hq >= p.kv_mul) continue;
-      float M = -INFINITY, L = 0.f;
-      float O[DPT];
+    // release our writes, acquire the other arrivals' (device scope, cumulative over the warp);
+    // true in the warp that arrives last, which also resets the counter
+    auto arrive_last = [&](int* cnt, int expected) -> bool {
+      int prev = 0;
+      if (lane == 0)
+        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(prev) : "l"(cnt) : "memory");
+      prev = __shfl_sync(0xffffffffu, prev, 0);
+      if (prev != expected - 1) return false;
+      if (lane == 0) *cnt = 0;
+      __syncwarp();
+      return true;
+    };
+    auto slot_of = [&](int64_t c) {  // only the first piece can be a "tail" slot
+      return p.partials + ((c == c_first) ? 2 * c + 1 : 2 * c) * C::kPartialFloats;
+    };
+    // Merges n slots into the item's output rows (dst == nullptr) or into one unnormalised slot.
+    // Token group tg handles the heads j with j % TG == tg, lane `sub` its DPT dims.  The
+    // weights 2^(m_c - M) need the overall maximum first; with M known every slot's term is
+    // independent, so the loads of the accumulation loop can be in flight together.
+    // The LPT lanes of a token group walk the head loop together (same j, same trip count);
+    // other groups may be elsewhere, so the shuffles name only the group's own lanes.
+    const uint32_t group_mask = (LPT == 32 ? 0xffffffffu : ((1u << LPT) - 1u)) << (tg * LPT);
+    auto merge = [&](int64_t n, auto slot_fn, float* dst) {
+      for (int j = tg; j < QH; j += TG) {
+        const int hq = hg * QH + j;
+        if (hq >= p.kv_mul) continue;
+        float M = -INFINITY;
+        for (int64_t i = sub; i < n; i += LPT) M = fmaxf(M, __ldcg(slot_fn(i) + QH * kD + j));
 #pragma unroll
-      for (int e = 0; e < DPT; ++e) O[e] = 0.f;
-#pragma unroll 2
-      for (int64_t c = c_first; c <= c_last; ++c) {
-        // only the first piece can be a "tail" slot
-        const float* ps = p.partials + ((c == c_first) ? 2 * c + 1 : 2 * c) * C::kPartialFloats;
-        const float mw = __ldcg(ps + QH * kD + j), lw = __ldcg(ps + QH * kD + QH + j);
-        float4 v[DPT / 4];
-#pragma unroll
-        for (int k = 0; k < DPT / 4; ++k)
-          v[k] = __ldcg(reinterpret_cast<const float4*>(ps + j * kD + coff[(k * 4) / E] / C::kEltB + (k * 4) % E));
-        const float Mn = fmaxf(M, mw);
-        const float a = fast_exp2(M - Mn), bsc = fast_exp2(mw - Mn);
-        L = L * a + lw * bsc;
-#pragma unroll
-        for (int k = 0; k < DPT / 4; ++k) {
-          O[4 * k + 0] = O[4 * k + 0] * a + v[k].x * bsc;
-          O[4 * k + 1] = O[4 * k + 1] * a + v[k].y * bsc;
-          O[4 * k + 2] = O[4 * k + 2] * a + v[k].z * bsc;
-          O[4 * k + 3] = O[4 * k + 3] * a + v[k].w * bsc;
+        for (int m = 1; m < LPT; m <<= 1) M = fmaxf(M, __shfl_xor_sync(group_mask, M, m));
+        float L = 0.f;
+        for (int64_t i = sub; i < n; i += LPT) {
+          const float* ps = slot_fn(i);
+          L += __ldcg(ps + QH * kD + QH + j) * fast_exp2(__ldcg(ps + QH * kD + j) - M);
         }
-        M = Mn;
-      }
-      uint8_t* o = reinterpret_cast<uint8_t*>(static_cast<T*>(p.out) + int64_t(item.b) * p.num_q_heads * kD +
-                                              int64_t(item.kvh * p.kv_mul + hq) * kD);
-      const float inv = 1.f / L;
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) {
-        __align__(16) T tmp[E];
+        for (int m = 1; m < LPT; m <<= 1) L += __shfl_xor_sync(group_mask, L, m);
+        float O[DPT];
 #pragma unroll
-        for (int e = 0; e < E; ++e) tmp[e] = Elt<T>::from_float(O[c * E + e] * inv);
-        *reinterpret_cast<uint4*>(o + coff[c]) = *reinterpret_cast<const uint4*>(tmp);
+        for (int e = 0; e < DPT; ++e) O[e] = 0.f;
+#pragma unroll 4
+        for (int64_t i = 0; i < n; ++i) {
+          const float* ps = slot_fn(i);
+          const float w = fast_exp2(__ldcg(ps + QH * kD + j) - M);
+#pragma unroll
+          for (int k = 0; k < DPT / 4; ++k) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(ps + j * kD + coff[(k * 4) / E] / C::kEltB + (k * 4) % E));
+            O[4 * k + 0] = fmaf(v.x, w, O[4 * k + 0]);
+            O[4 * k + 1] = fmaf(v.y, w, O[4 * k + 1]);
+            O[4 * k + 2] = fmaf(v.z, w, O[4 * k + 2]);
+            O[4 * k + 3] = fmaf(v.w, w, O[4 * k + 3]);
+          }
+        }
+        if (dst) {
+#pragma unroll
+          for (int k = 0; k < DPT / 4; ++k)
+            *reinterpret_cast<float4*>(dst + j * kD + coff[(k * 4) / E] / C::kEltB + (k * 4) % E) =
+                make_float4(O[4 * k + 0], O[4 * k + 1], O[4 * k + 2], O[4 * k + 3]);
+          if (sub == 0) {
+            dst[QH * kD + j] = M;
+            dst[QH * kD + QH + j] = L;
+          }
+        } else {
+          uint8_t* o = reinterpret_cast<uint8_t*>(static_cast<T*>(p.out) + int64_t(item.b) * p.num_q_heads * kD +
+                                                  int64_t(item.kvh * p.kv_mul + hq) * kD);
+          const float inv = 1.f / L;
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) {
+            __align__(16) T tmp[E];
+#pragma unroll
+            for (int e = 0; e < E; ++e) tmp[e] = Elt<T>::from_float(O[c * E + e] * inv);
+            *reinterpret_cast<uint4*>(o + coff[c]) = *reinterpret_cast<const uint4*>(tmp);
+          }
+        }
       }
+    };
+    int* item_cnt = p.counters + (item.b * (p.num_kv_heads * p.head_groups) + item.sub);
+    // An item cut into many pieces (one very long sequence) is assembled in two levels so that
+    // no single warp reads them all: the pieces of kGroup consecutive warps are merged by the
+    // last of them to arrive into one slot of a second area, and the last group to finish
+    // merges those.  The second area sits at the end of the slot array: [group slots][one
+    // slot of group counters]; it is used only if the array has room for it.
+    constexpr int kGroup = 16, kFlatMax = 48;
+    const int64_t W_all = int64_t(gridDim.x) * C::kWarps;
+    const int64_t n_groups = (W_all + kGroup - 1) / kGroup;
+    const int64_t group_base = int64_t(p.partial_slots) - 1 - 2 * n_groups;  // first group slot
+    if (pieces <= kFlatMax || group_base < 2 * W_all || 2 * n_groups * 4 > int64_t(C::kPartialFloats) * 4) {
+      if (!arrive_last(item_cnt, pieces)) return;
+      // a handful of pieces: one pass with a running maximum
+      for (int j = tg; j < QH; j += TG) {
+        const int hq = hg * QH + j;
+        if (hq >= p.kv_mul) continue;
+        float M = -INFINITY, L = 0.f;
+        float O[DPT];
+#pragma unroll
+        for (int e = 0; e < DPT; ++e) O[e] = 0.f;
+#pragma unroll 2
+        for (int64_t c = c_first; c <= c_last; ++c) {
+          const float* ps = slot_of(c);
+          const float mw = __ldcg(ps + QH * kD + j), lw = __ldcg(ps + QH * kD + QH + j);
+          float4 v[DPT / 4];
+#pragma unroll
+          for (int k = 0; k < DPT / 4; ++k)
+            v[k] = __ldcg(reinterpret_cast<const float4*>(ps + j * kD + coff[(k * 4) / E] / C::kEltB + (k * 4) % E));
+          const float Mn = fmaxf(M, mw);
+          const float a = fast_exp2(M - Mn), bsc = fast_exp2(mw - Mn);
+          L = L * a + lw * bsc;
+#pragma unroll
+          for (int k = 0; k < DPT / 4; ++k) {
+            O[4 * k + 0] = O[4 * k + 0] * a + v[k].x * bsc;
+            O[4 * k + 1] = O[4 * k + 1] * a + v[k].y * bsc;
+            O[4 * k + 2] = O[4 * k + 2] * a + v[k].z * bsc;
+            O[4 * k + 3] = O[4 * k + 3] * a + v[k].w * bsc;
+          }
+          M = Mn;
+        }
+        uint8_t* o = reinterpret_cast<uint8_t*>(static_cast<T*>(p.out) + int64_t(item.b) * p.num_q_heads * kD +
+                                                int64_t(item.kvh * p.kv_mul + hq) * kD);
+        const float inv = 1.f / L;
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          __align__(16) T tmp[E];
+#pragma unroll
+          for (int e = 0; e < E; ++e) tmp[e] = Elt<T>::from_float(O[c * E + e] * inv);
+          *reinterpret_cast<uint4*>(o + coff[c]) = *reinterpret_cast<const uint4*>(tmp);
+        }
+      }
+      return;
     }
+    // A group holds pieces of at most two such items: one that entered it from the left (0) and
+    // one that starts inside it (1).
+    auto group_slot = [&](int64_t g) {
+      return p.partials + (group_base + 2 * g + ((c_first < g * kGroup) ? 0 : 1)) * C::kPartialFloats;
+    };
+    const int64_t g = worker / kGroup;
+    const int64_t g_lo = c_first > g * kGroup ? c_first : g * kGroup;
+    const int64_t g_hi = c_last < g * kGroup + kGroup - 1 ? c_last : g * kGroup + kGroup - 1;
+    int* group_cnt = reinterpret_cast<int*>(p.partials + (int64_t(p.partial_slots) - 1) * C::kPartialFloats) +
+                     2 * g + ((c_first < g * kGroup) ? 0 : 1);
+    if (!arrive_last(group_cnt, int(g_hi - g_lo) + 1)) return;
+    merge(g_hi - g_lo + 1, [&](int64_t i) { return slot_of(g_lo + i); }, group_slot(g));
+    __syncwarp();  // every lane's part of the group slot is ordered before lane 0's release
+    const int64_t G0 = c_first / kGroup, G1 = c_last / kGroup;
+    if (arrive_last(item_cnt, int(G1 - G0) + 1))
+      merge(G1 - G0 + 1, [&](int64_t i) { return static_cast<const float*>(group_slot(G0 + i)); }, nullptr);
   };
 
   auto wait_slot = [&](uint64_t* bar, uint32_t ph) -> bool {
@@ -765,6 +863,7 @@ int kpx::decode_rows(void* out, const void* q, const void* k_pool, const void* v
   p.num_kv_heads = layout->num_kv_heads;
   p.kv_mul = num_q_heads / layout->num_kv_heads;
   p.head_groups = 1;
+  p.partial_slots = 2 * kMaxSms * kMaxWarpsPerCta;
   p.tile_contig = tile_contiguous(layout) ? 1 : 0;
   p.qscale = scale * kLog2e;
   // the block prefix of one launch lives in shared memory: long batches go in slices
@@ -849,6 +948,13 @@ extern "C" int kpx_paged_decode_static(void* out, const void* q, const void* k_p
   // The array keeps whatever the previous call left: the status word and the piece
   // counters must start at zero (partials are always written before they are read).
   KPX_CUDA_TRY(cudaMemsetAsync(scratch, 0, size_t(kStatusBytes + kStaticCounterBytes), s));
+  {
+    // the group counters of the two-level assembly live in the last partial slot
+    const int qh = heads_per_warp(num_q_heads / layout->num_kv_heads);
+    const size_t slot_bytes = size_t(qh * kD + 8) * sizeof(float);
+    uint8_t* partials = static_cast<uint8_t*>(scratch) + kStatusBytes + counter_bytes(num_q_heads, layout->num_kv_heads);
+    KPX_CUDA_TRY(cudaMemsetAsync(partials + size_t(2 * kMaxSms * kMaxWarpsPerCta - 1) * slot_bytes, 0, slot_bytes, s));
+  }
   return kpx_paged_decode(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq,
                           seq_lens, len_bias, batch, num_q_heads, scale, scratch,
                           kStaticScratchBytes, stream);

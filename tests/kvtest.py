@@ -34,6 +34,7 @@ class Oracle:
             "orc_sin_cos_cache": [i32, i32, C.c_float, f32p, f32p],
             "orc_rope": [i32, i32, i32, C.c_void_p, C.c_void_p, i32, f32p, f32p],
             "orc_rope_batched": [i32, i32, i32, i32, i32, C.c_void_p, C.c_void_p, f32p, f32p],
+            "orc_rmsnorm_heads": [C.c_void_p, C.c_int64, i32, i32, C.c_void_p, C.c_float],
             "orc_softmax_inplace": [f32p, i32],
             "orc_mha": [i32, i32, i32, i32, i32, i32, i32, f32p, f32p, f32p, f32p, f32p],
             "orc_mha_f64": [i32, i32, i32, i32, i32, i32, i32, f64p, f32p, f32p, f32p],
@@ -64,6 +65,11 @@ class Oracle:
         self.lib.orc_rope_batched(start_pos, n, dim, kv_dim, head_size,
                                   q.ctypes.data if q is not None else None,
                                   k.ctypes.data if k is not None else None, sin, cos)
+
+    def rmsnorm_heads(self, x, heads, head_size, weight, eps=1e-6):
+        """x [rows, heads*head_size] float32, normalised per head in place."""
+        self.lib.orc_rmsnorm_heads(x.ctypes.data, x.shape[0], heads, head_size,
+                                   np.ascontiguousarray(weight, np.float32).ctypes.data, eps)
 
     def rope(self, pos, q, k, head_size, sin, cos):
         dim = q.shape[0] if q is not None else k.shape[0]

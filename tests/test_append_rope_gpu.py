@@ -84,6 +84,62 @@ def test_rope_append_bit_exact(native_libs, oracle, dtype):
     assert np.array_equal(kvtest.from_device(vp, dtype).view(np.uint8), vp_ref.view(np.uint8))
 
 
+@pytest.mark.parametrize("dtype", ["f16", "bf16", "f32"])
+@pytest.mark.parametrize("which", ["both", "k_only"])
+def test_norm_rope_append_matches_oracle(native_libs, oracle, dtype, which):
+    """Per-head RMSNorm (Qwen3 q/k norm) fused in front of RoPE + append.  The sum of squares is
+    a tree over lanes on the device and sequential in the oracle, so rows agree to a few fp32
+    ulps before the one rounding to the cache dtype: at most one ulp of that dtype apart.  The
+    pool rows are bit-identical to the K rows the call returns, V rows are copied untouched."""
+    import torch
+    from orinmllm_b200 import capi
+    H, HKV, D = 16, 4, 128
+    n, start = 37, 5
+    rng = np.random.default_rng(12)
+    sin, cos = oracle.sin_cos_cache(D, 64, 1e6)
+    q32 = rng.standard_normal((n, H * D)).astype(np.float32) * 3.0
+    k32 = rng.standard_normal((n, HKV * D)).astype(np.float32) * 0.2
+    v32 = rng.standard_normal((n, HKV * D)).astype(np.float32)
+    wq = (1.0 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    wk = (1.0 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    q_st, k_st, v_st = (kvtest.to_storage(x, dtype) for x in (q32, k32, v32))
+    q_ref = kvtest.storage_to_f32(q_st, dtype).copy()
+    k_ref = kvtest.storage_to_f32(k_st, dtype).copy()
+    if which == "both":
+        oracle.rmsnorm_heads(q_ref, H, D, wq, 1e-6)
+    oracle.rmsnorm_heads(k_ref, HKV, D, wk, 1e-6)
+    oracle.rope_batched(start, q_ref, k_ref, D, sin, cos)
+    nblk = 6
+    perm = rng.permutation(nblk).astype(np.int64)
+    pos = np.arange(start, start + n)
+    slots = perm[pos // 16] * 16 + pos % 16
+    shape = (nblk, HKV, 16, D)
+    lay = capi.layout_paged(capi.dtype_code(kvtest.torch_dtype(dtype)), HKV, D, 16, nblk)
+    dq, dk, dv = (kvtest.to_device(x, dtype) for x in (q_st, k_st, v_st))
+    kp = kvtest.to_device(kvtest.poison(shape, dtype), dtype)
+    vp = kvtest.to_device(kvtest.poison(shape, dtype), dtype)
+    capi.norm_rope_append(dq, dk, dv, H, torch.from_numpy(wq).cuda() if which == "both" else None,
+                          torch.from_numpy(wk).cuda(), 1e-6, torch.from_numpy(pos.astype(np.int32)).cuda(),
+                          torch.from_numpy(sin).cuda(), torch.from_numpy(cos).cuda(), kp, vp, lay,
+                          torch.from_numpy(slots).cuda(), n)
+    got_q = kvtest.storage_to_f32(kvtest.from_device(dq, dtype), dtype)
+    got_k = kvtest.storage_to_f32(kvtest.from_device(dk, dtype), dtype)
+    ulp = {"f16": 2.0 ** -10, "bf16": 2.0 ** -7, "f32": 2.0 ** -21}[dtype]  # one ulp, relative, with slack for fp32
+    for got, ref, name in ((got_q, q_ref, "q"), (got_k, k_ref, "k")):
+        err = np.abs(got - ref)
+        bound = ulp * np.maximum(np.abs(ref), 1e-3) + 1e-6
+        assert np.all(err <= bound), f"{name}: worst {float((err / bound).max()):.2f} x bound"
+    # the pool holds exactly the K rows the call returned, and the V rows as given
+    kp_ref, vp_ref = kvtest.poison(shape, dtype), kvtest.poison(shape, dtype)
+    oracle.append_paged(kp_ref, kvtest.from_device(dk, dtype), slots, HKV, D, 16)
+    oracle.append_paged(vp_ref, v_st, slots, HKV, D, 16)
+    assert np.array_equal(kvtest.from_device(kp, dtype).view(np.uint8), kp_ref.view(np.uint8))
+    assert np.array_equal(kvtest.from_device(vp, dtype).view(np.uint8), vp_ref.view(np.uint8))
+    # a normalised head has mean square ~ mean(w^2) before the rotation, which preserves it
+    ms = (got_k.reshape(n, HKV, D) ** 2).mean(-1)
+    assert np.allclose(ms, (wk ** 2).mean(), rtol=0.2)
+
+
 def test_sin_cos_cache_close_to_cpu_table(native_libs, oracle):
     import torch
     from orinmllm_b200 import capi

@@ -7,7 +7,7 @@ from tests import kvtest
 pytestmark = pytest.mark.gpu
 
 
-def _run_case(oracle, case, check_append=True):
+def _run_case(oracle, case, check_append=True, launches=1):
     import torch
     from orinmllm_b200 import capi
 
@@ -31,10 +31,17 @@ def _run_case(oracle, case, check_append=True):
     nbytes = capi.decode_workspace_bytes(b, case.q_heads, case.kv_heads, case.head_size)
     ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
     capi.workspace_init(ws, nbytes)
-    capi.paged_decode(out, q, kp, vp, lay, torch.from_numpy(case.block_table).cuda(),
-                      case.block_table.shape[1], torch.from_numpy(case.seq_lens).cuda(), 0, b,
-                      case.q_heads, 1.0 / np.sqrt(case.head_size), ws, nbytes)
-    assert capi.workspace_status(ws) == 0
+    first = None
+    for _ in range(launches):  # later launches reuse the workspace as the earlier ones left it
+        out.fill_(float("nan"))
+        capi.paged_decode(out, q, kp, vp, lay, torch.from_numpy(case.block_table).cuda(),
+                          case.block_table.shape[1], torch.from_numpy(case.seq_lens).cuda(), 0, b,
+                          case.q_heads, 1.0 / np.sqrt(case.head_size), ws, nbytes)
+        assert capi.workspace_status(ws) == 0
+        if first is None:
+            first = out.clone()
+        else:
+            assert torch.equal(first.view(torch.uint8), out.view(torch.uint8)), "a repeated launch differs"
     got = kvtest.storage_to_f32(kvtest.from_device(out, dt), dt)
     ref = kvtest.oracle_decode(oracle, case, kp_ref, vp_ref, threads=oracle.max_threads())
     return kvtest.assert_attention_close(got, ref, f"decode {dt} H={case.q_heads}/{case.kv_heads}", dt)
@@ -59,6 +66,15 @@ def test_decode_single_long(native_libs, oracle):
     # one sequence spread over every persistent CTA: exercises the split-KV merge
     case = kvtest.make_paged_case(7, "f16", 32, 8, [20000])
     _run_case(oracle, case)
+
+
+@pytest.mark.parametrize("dtype,heads", [("f16", (8, 2)), ("bf16", (14, 2)), ("f16", (2, 2))])
+def test_decode_long_items_two_level_assembly(native_libs, oracle, dtype, heads):
+    """Sequences long enough that one (sequence, KV head) item is cut into hundreds of pieces: the
+    pieces are merged per group of warps and then per item.  Launched three times on the same
+    workspace (the counters of both levels must have reset themselves)."""
+    case = kvtest.make_paged_case(5, dtype, heads[0], heads[1], [60000, 17, 45000, 3000])
+    _run_case(oracle, case, check_append=False, launches=3)
 
 
 def test_decode_many_short(native_libs, oracle):

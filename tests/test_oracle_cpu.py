@@ -109,3 +109,15 @@ def test_prefill_oracle_is_causal(oracle):
     assert np.array_equal(out, out2)
     one = oracle.mha(16 + 3, H, 0, S, HKV * D, 2, D, q[3], kc.reshape(-1), vc.reshape(-1))
     assert np.array_equal(out[3], one)
+
+
+def test_rmsnorm_heads_definition(oracle):
+    """w * x / sqrt(mean(x^2) + eps) per head row (cpu/rmsnorm_kernel.cpp:26-34)."""
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((5, 3 * 128)).astype(np.float32)
+    w = rng.standard_normal(128).astype(np.float32)
+    ref = x.reshape(5, 3, 128).astype(np.float64)
+    ref = w * ref / np.sqrt((ref ** 2).mean(-1, keepdims=True) + 1e-6)
+    got = x.copy()
+    oracle.rmsnorm_heads(got, 3, 128, w, 1e-6)
+    assert np.allclose(got.reshape(5, 3, 128), ref, rtol=2e-6, atol=1e-6)
