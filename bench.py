@@ -102,7 +102,9 @@ class DecodeWorkload:
         import torch
         from orinmllm_b200 import capi
         self.torch, self.capi, self.dev = torch, capi, device
-        self.lens0 = make_lens(SEED + 1000 * rank)
+        # weak scaling: every GPU gets the same amount of work (the same context lengths); block
+        # placement and data differ per rank
+        self.lens0 = make_lens(SEED)
         rng = np.random.default_rng(SEED + 1000 * rank + 1)
         final = self.lens0 + total_steps
         nblk = (final + BLOCK - 1) // BLOCK
