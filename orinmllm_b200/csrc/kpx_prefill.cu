@@ -15,6 +15,7 @@ int prefill_tc(void* out, const void* q, const void* k_pool, const void* v_pool,
                const int32_t* block_table, int32_t max_blocks_per_seq, const int32_t* cu_q_lens_host,
                const int32_t* start_pos_host, int32_t batch, int32_t num_q_heads, float scale, void* tile_area,
                int64_t tile_area_bytes, int32_t* status, cudaStream_t stream);
+int64_t prefill_tc_area_bytes(int32_t total_q, int32_t num_q_heads);
 namespace {
 
 // 0 = tensor-core tiles where the layout allows, else per-query streaming; 1 = always streaming
@@ -48,11 +49,7 @@ extern "C" __attribute__((visibility("default"))) void kpx_internal_set_prefill_
   g_prefill_path = v;
 }
 
-// Work list of the tensor-core path: at most one 40-byte entry per (128-row query tile, query
-// head), and there are never more tiles than query tokens.
-static int64_t tile_area_bytes(int32_t total_q, int32_t num_q_heads) {
-  return align256((int64_t(total_q) + 1) * int64_t(num_q_heads > 0 ? num_q_heads : 1) * 40);
-}
+static int64_t tile_area_bytes(int32_t total_q, int32_t num_q_heads) { return prefill_tc_area_bytes(total_q, num_q_heads); }
 
 extern "C" int64_t kpx_prefill_workspace_bytes(int32_t total_q, int32_t num_q_heads,
                                                int32_t num_kv_heads, int32_t head_size) {

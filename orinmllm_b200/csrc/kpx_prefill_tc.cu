@@ -42,12 +42,30 @@ struct PairDesc {
   int32_t seq;  // row of the block table
   int32_t kvh;
   ItemDesc it[2];
+  // This CTA's share of the pair's key tiles [tile0, tile1) and, when the pair is cut into
+  // several such shares, the slot its unnormalised result goes to (-1: the CTA owns the whole
+  // pair and writes the output rows itself).
+  int32_t tile0, tile1, part, pad;
 };
+// One item whose key range was cut: `parts` slots to merge into its output rows.
+struct MergeDesc {
+  ItemDesc it;
+  int32_t slot[4];
+  int32_t parts, x;  // x: which item of its pair (position inside the slot)
+  int32_t pad[2];
+};
+// A slot holds, for both items of a pair, 128 rows of [O (128 floats), m, l].
+constexpr int kPartRow = kD + 2;
+constexpr int64_t kPartItemFloats = int64_t(kTile) * kPartRow;
+constexpr int64_t kPartSlotFloats = 2 * kPartItemFloats;
+constexpr int kMaxPartSlots = 320;  // two per SM of the largest device planned for
+inline int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
 
 struct PrefillParams {
   void* out;
   const int32_t* block_table;
   const PairDesc* pairs;
+  float* partials;  // slots of kPartSlotFloats floats
   int32_t* status;
   int64_t num_blocks;
   int32_t max_blocks_per_seq, num_q_heads, kv_mul;
@@ -312,13 +330,13 @@ struct RowState {
 // log2 units): weights stay below 2^8, and O is rescaled in far fewer tiles.
 constexpr float kLazyMax = 8.f;
 
-// Softmax of tile j of one item: S (tensor memory, 128 columns at tS) -> P over S, O rescaled
-// where the row maximum moved.  Called by the 256 softmax threads of the item (contains their
+// Softmax of key tile j of one item: S (tensor memory, 128 columns at tS) -> P over S, O (which
+// holds something when has_o) rescaled where the row maximum moved.  Called by the 256 softmax threads of the item (contains their
 // barrier `bar_id`).
 template <typename T>
 __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t lane_addr, int row, int half,
-                                             float qscale, int j, int pos0, float* s_half, int bar_id,
-                                             RowState& st) {
+                                             float qscale, int j, bool has_o, int pos0, float* s_half,
+                                             int bar_id, RowState& st) {
   const int my_pos = pos0 + row;
   const bool diag = (j * kTile + kTile - 1) > pos0;  // some row of this item is masked in this tile
   const int limit0 = my_pos - (j * kTile + half * 64);   // keys e > limit are newer than the query
@@ -349,7 +367,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t 
     weights32<T, false>(tS + lane_addr + 32, r1, qscale, neg_m, 0, st.l);
   }
   // O += P V of the previous tile has completed (the MMA that produced S was issued after it)
-  if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+  if (has_o && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
       tmem_ld32(tO + lane_addr + c * 32, r0);
@@ -390,6 +408,71 @@ __device__ __forceinline__ void write_item(uint32_t tO, uint32_t lane_addr, int 
   }
 }
 
+// The same rows, unnormalised, for a CTA that saw only part of the keys: [O (128), m, l] per row
+// into its slot; the merge kernel combines the parts.
+__device__ __forceinline__ void write_partial(uint32_t tO, uint32_t lane_addr, int row, int half, float* dst,
+                                              float* s_half, int bar_id, const RowState& st) {
+  const float l_mine = st.l.x + st.l.y;
+  softmax_sync(bar_id);  // earlier readers of the exchange area are done
+  s_half[half * kTile + row] = l_mine;
+  softmax_sync(bar_id);
+  float* drow = dst + int64_t(row) * kPartRow;
+  if (half == 0) {
+    drow[kD] = st.m;
+    drow[kD + 1] = l_mine + s_half[kTile + row];
+  }
+  uint32_t r[32];
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    tmem_ld32(tO + lane_addr + c * 32, r);
+#pragma unroll
+    for (int v = 0; v < 16; ++v)  // rows are 130 floats long: 8-byte alignment only
+      *reinterpret_cast<uint2*>(drow + half * 64 + c * 32 + 2 * v) = make_uint2(r[2 * v], r[2 * v + 1]);
+  }
+}
+
+// Output rows of an item whose keys were cut into parts: out = sum_p 2^(m_p - M) O_p / sum_p 2^(m_p - M) l_p.
+// blockIdx.x = item, blockIdx.y = group of 16 rows; threadIdx.x = d, threadIdx.y takes every 4th row.
+constexpr int kMergeRowsPerCta = 16, kMergeRowLanes = 4;
+template <typename T>
+__global__ void __launch_bounds__(kD* kMergeRowLanes)
+    prefill_merge_kernel(T* __restrict__ out, const float* __restrict__ partials, const MergeDesc* __restrict__ descs,
+                         int num_q_heads) {
+  const MergeDesc md = descs[blockIdx.x];
+  const int d = threadIdx.x;
+#pragma unroll
+  for (int i = 0; i < kMergeRowsPerCta / kMergeRowLanes; ++i) {
+    const int row = blockIdx.y * kMergeRowsPerCta + i * kMergeRowLanes + threadIdx.y;
+    if (row >= md.it.nrows) continue;
+    // every part's (m, l) first, then the weights, then the O values: two rounds of independent
+    // loads.  A part in which the row saw no key (l = 0) carries a placeholder maximum and does
+    // not count.
+    const float* base = partials + md.x * kPartItemFloats + int64_t(row) * kPartRow;
+    float mp[4], lp[4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const bool on = p < md.parts;
+      const float* prow = base + (on ? md.slot[p] : md.slot[0]) * kPartSlotFloats;
+      mp[p] = prow[kD];
+      lp[p] = on ? prow[kD + 1] : 0.f;
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+      if (lp[p] > 0.f) M = fmaxf(M, mp[p]);
+    float acc = 0.f, L = 0.f;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const float w = lp[p] > 0.f ? fast_exp2(mp[p] - M) : 0.f;
+      const float* prow = base + (p < md.parts ? md.slot[p] : md.slot[0]) * kPartSlotFloats;
+      const float o = prow[d];
+      acc = lp[p] > 0.f ? fmaf(o, w, acc) : acc;  // (a skipped part may hold anything, NaN included)
+      L = fmaf(lp[p], w, L);
+    }
+    out[(int64_t(md.it.row0 + row) * num_q_heads + md.it.head) * kD + d] = Elt<T>::from_float(L > 0.f ? acc / L : 0.f);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
     prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q,
@@ -417,8 +500,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   const PairDesc pd = p.pairs[blockIdx.x];
   const int last_pos = pd.it[1].pos0 + pd.it[1].nrows - 1;  // newest position any row of the pair may see
   const int kv_len = last_pos + 1;
-  const int nB = last_pos / kTile + 1;                       // key tiles 0 .. nB-1
-  const int nA = pd.it[0].nrows > 0 ? (pd.it[0].pos0 + pd.it[0].nrows - 1) / kTile + 1 : 0;  // <= nB
+  const int tilesB = last_pos / kTile + 1;                   // key tiles 0 .. tilesB-1 of item 1
+  const int tilesA = pd.it[0].nrows > 0 ? (pd.it[0].pos0 + pd.it[0].nrows - 1) / kTile + 1 : 0;  // <= tilesB
+  // this CTA walks the key tiles j0 + j, j = 0 .. nB-1 (item 0: .. nA-1)
+  const int j0 = pd.tile0;
+  const int nB = min(tilesB, pd.tile1) - j0;
+  const int nA = max(0, min(tilesA, pd.tile1) - j0);
   const bool ragged = (kv_len % kTile) != 0;                 // the last tile has rows past the newest token
 
   if (tid == 0) {
@@ -439,7 +526,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_arrive_expect_tx(q_full, (nA > 0 ? 2u : 1u) * kOperandB);
 #pragma unroll
       for (int x = 0; x < 2; ++x)
-        if (pd.it[x].nrows > 0) {
+        if ((x ? nB : nA) > 0) {
           tma_load_3d(sQ + x * kOperandB, &map_q, 0, pd.it[x].head, pd.it[x].row0, q_full);
           tma_load_3d(sQ + x * kOperandB + kChunkB, &map_q, 64, pd.it[x].head, pd.it[x].row0, q_full);
         }
@@ -447,12 +534,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool ok = true;
     for (int j = 0; j < nB && ok; ++j) {
       const int stage = j & 1, use = j >> 1;
-      const int left = kv_len - j * kTile;                        // tokens from the start of this tile
+      const int left = kv_len - (j0 + j) * kTile;                 // tokens from the start of this tile
       const int nblk = left >= kTile ? kTile / kBS : (left + kBS - 1) / kBS;
       // lanes 0..15: block (lane >> 1), 64-element slab (lane & 1)
       int id = 0;
       if (lane < 2 * nblk) {
-        id = __ldg(table + j * (kTile / kBS) + (lane >> 1));
+        id = __ldg(table + (j0 + j) * (kTile / kBS) + (lane >> 1));
         if (id < 0 || (p.num_blocks > 0 && id >= p.num_blocks)) {
           atomicMax(p.status, KPX_ERR_INVALID_ARGUMENT);
           id = 0;
@@ -472,7 +559,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           tma_load_4d(dst, kv ? &map_v : &map_k, (lane & 1) * 64, 0, pd.kvh, id, full);
         }
       }
-      if (ok && ragged && j == nB - 1) {
+      if (ok && ragged && j0 + j == tilesB - 1) {
         // V rows past the newest token must be zero (a weight of 0 times pool garbage must stay
         // 0); the boxes have to land first because the last one covers some of these rows
         ok = wait_or_abort(v_full + stage, uint32_t(use & 1), abort_flag);
@@ -534,7 +621,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // K(j) / V(j) of stage j&1 are in their (j>>1)-th use; the last tile also waits for the zeroed tail
     auto wait_k = [&](int j) { return wait(k_full + (j & 1), (j >> 1) & 1); };
     auto wait_v = [&](int j) {
-      if (ragged && j == nB - 1 && !wait(tail_ok, 0)) return false;
+      if (ragged && j0 + j == tilesB - 1 && !wait(tail_ok, 0)) return false;
       return wait(v_full + (j & 1), (j >> 1) & 1);
     };
     if (wait(q_full, 0) && wait_k(0)) {
@@ -584,6 +671,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     // O, the second columns 64..127 =====
     const int x = warp >> 3;                      // item
     const int n_mine = x ? nB : nA;
+    if (n_mine == 0 && pd.part >= 0 && pd.it[x].nrows > 0) {
+      // this part holds none of the item's keys: a row sum of 0 tells the merge to skip it
+      const int t = tid & 255;
+      if (t < kTile) p.partials[pd.part * kPartSlotFloats + x * kPartItemFloats + int64_t(t) * kPartRow + kD + 1] = 0.f;
+    }
     if (n_mine > 0) {
       const int t = tid & 255, row = t & 127, half = t >> 7;
       const uint32_t lane_addr = (uint32_t((warp & 3) * 32) << 16) + uint32_t(half * 64);
@@ -601,14 +693,19 @@ __global__ void __launch_bounds__(kThreads, 1)
       };
       for (int j = 0; j < n_mine; ++j) {
         if (!wait_all(s_full + x, j & 1)) break;
-        softmax_tile<T>(tS, tO, lane_addr, row, half, p.qscale, j, it.pos0, my_half, bar_id, st);
+        softmax_tile<T>(tS, tO, lane_addr, row, half, p.qscale, j0 + j, j > 0, it.pos0, my_half, bar_id, st);
         // this warp's part of P is in tensor memory
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_full + x);
       }
-      if (!failed && wait_all(o_full + x, 0))
-        write_item<T>(tO, lane_addr, row, half, it, p.num_q_heads, p.out, my_half, bar_id, st);
+      if (!failed && wait_all(o_full + x, 0)) {
+        if (pd.part < 0)
+          write_item<T>(tO, lane_addr, row, half, it, p.num_q_heads, p.out, my_half, bar_id, st);
+        else
+          write_partial(tO, lane_addr, row, half, p.partials + pd.part * kPartSlotFloats + x * kPartItemFloats,
+                        my_half, bar_id, st);
+      }
     }
   }
 
@@ -651,6 +748,9 @@ bool make_map(CUtensorMap* map, int32_t dtype, const void* base, int rank, const
 }
 }  // namespace
 
+// -1: cut underfilled calls (default); 0: never; 2..4: always, into that many parts (tests).
+int g_prefill_split = -1;
+
 // Host side: pair list -> workspace, tensor maps, launch.  Returns KPX_ERR_UNIMPLEMENTED when
 // the layout, dtype or scale is outside this path so that the caller can fall back to the
 // streaming path.
@@ -672,7 +772,7 @@ int prefill_tc(void* out, const void* q, const void* k_pool, const void* v_pool,
     const int32_t n = cu_q_lens_host[b + 1] - cu_q_lens_host[b];
     if (n <= 0) continue;
     for (int32_t kvh = 0; kvh < layout->num_kv_heads; ++kvh) {
-      PairDesc pd{b, kvh, {{0, 0, 0, 0}, {0, 0, 0, 0}}};
+      PairDesc pd{b, kvh, {{0, 0, 0, 0}, {0, 0, 0, 0}}, 0, 1 << 30, -1, 0};
       int held = 0;
       for (int32_t t0 = 0; t0 < n; t0 += kTile)
         for (int32_t h = kvh * kv_mul; h < (kvh + 1) * kv_mul; ++h) {
@@ -697,7 +797,68 @@ int prefill_tc(void* out, const void* q, const void* k_pool, const void* v_pool,
     return tiles(d.it[0]) + tiles(d.it[1]);
   };
   std::stable_sort(pairs.begin(), pairs.end(), [&](const PairDesc& a, const PairDesc& b) { return cost(a) > cost(b); });
-  if (int64_t(pairs.size() * sizeof(PairDesc)) > tile_area_bytes) return KPX_ERR_WORKSPACE_TOO_SMALL;
+  // One CTA per SM: a call with fewer pairs than a third of the SMs leaves most of them idle.
+  // Its pairs are then cut along the keys into k = 3 or 4 parts that run side by side, each
+  // leaving unnormalised rows in a slot, and a small kernel merges them (one 4096-token prompt
+  // in chunks of 256: 927 -> 674 us per layer).  Measured and dropped: cutting in two when half
+  // the SMs are idle (the slots, the merge launch and the fixed cost of a CTA, about 7 us, eat
+  // the gain: 160 -> 205 us for one 2048-token prompt), and cutting the thin last wave of a
+  // larger call (the parts queue behind the first wave anyway).
+  std::vector<MergeDesc> merges;
+  {
+    const int sms = device_info().sm_count > 0 ? device_info().sm_count : 148;
+    const int n = int(pairs.size());
+    const int tail = (n < sms || g_prefill_split >= 2) ? n : 0;
+    int k = tail > 0 ? sms / tail : 1;
+    if (k > 4) k = 4;
+    if (k < 3) k = 1;
+    if (g_prefill_split == 0) k = 1;            // test knob: never cut
+    if (g_prefill_split >= 2) k = g_prefill_split > 4 ? 4 : g_prefill_split;  // test knob: always cut
+    if (k >= 2) {
+      std::vector<PairDesc> parts;
+      int slot = 0;
+      for (int i = n - tail; i < n; ++i) {
+        const PairDesc& d = pairs[size_t(i)];
+        auto tiles = [](const ItemDesc& it) { return it.nrows > 0 ? (it.pos0 + it.nrows - 1) / kTile + 1 : 0; };
+        const int tb = tiles(d.it[1]), ta = tiles(d.it[0]);
+        // every part gets at least one key tile of item 1; item 0 (never more tiles) may have none
+        // in the last parts and then leaves a row sum of 0 there
+        (void)ta;
+        const int kk = tb < k ? tb : k;
+        if (kk < 2 || slot + kk > kMaxPartSlots) {
+          parts.push_back(d);
+          continue;
+        }
+        MergeDesc m[2] = {};
+        for (int j = 0; j < kk; ++j) {
+          PairDesc c = d;
+          c.tile0 = tb * j / kk;
+          c.tile1 = tb * (j + 1) / kk;
+          c.part = slot;
+          for (int x = 0; x < 2; ++x) m[x].slot[j] = slot;
+          ++slot;
+          parts.push_back(c);
+        }
+        for (int x = 0; x < 2; ++x)
+          if (d.it[x].nrows > 0) {
+            m[x].it = d.it[x];
+            m[x].parts = kk;
+            m[x].x = x;
+            merges.push_back(m[x]);
+          }
+      }
+      pairs.resize(size_t(n - tail));
+      std::stable_sort(parts.begin(), parts.end(), [&](const PairDesc& a, const PairDesc& b) {
+        return (a.tile1 < (1 << 30) ? 2 * (a.tile1 - a.tile0) : cost(a)) > (b.tile1 < (1 << 30) ? 2 * (b.tile1 - b.tile0) : cost(b));
+      });
+      pairs.insert(pairs.end(), parts.begin(), parts.end());
+    }
+  }
+  // layout of the area: [pair list][merge list][part slots]
+  const int64_t pair_bytes = align256(int64_t(pairs.size()) * sizeof(PairDesc));
+  const int64_t merge_bytes = align256(int64_t(merges.size()) * sizeof(MergeDesc));
+  const int64_t slot_bytes = merges.empty() ? 0 : int64_t(kMaxPartSlots) * kPartSlotFloats * sizeof(float);
+  if (pair_bytes + merge_bytes + slot_bytes > tile_area_bytes) return KPX_ERR_WORKSPACE_TOO_SMALL;
 
   CUtensorMap map_q, map_k, map_v;
   {
@@ -718,8 +879,13 @@ int prefill_tc(void* out, const void* q, const void* k_pool, const void* v_pool,
         !make_map(&map_v, layout->dtype, v_pool, 4, dims, strides, box))
       return KPX_ERR_UNIMPLEMENTED;
   }
-  KPX_CUDA_TRY(cudaMemcpyAsync(tile_area, pairs.data(), pairs.size() * sizeof(PairDesc), cudaMemcpyHostToDevice, stream));
+  uint8_t* area = static_cast<uint8_t*>(tile_area);
+  KPX_CUDA_TRY(cudaMemcpyAsync(area, pairs.data(), pairs.size() * sizeof(PairDesc), cudaMemcpyHostToDevice, stream));
+  if (!merges.empty())
+    KPX_CUDA_TRY(cudaMemcpyAsync(area + pair_bytes, merges.data(), merges.size() * sizeof(MergeDesc),
+                                 cudaMemcpyHostToDevice, stream));
   PrefillParams p;
+  p.partials = reinterpret_cast<float*>(area + pair_bytes + merge_bytes);
   p.out = out;
   p.block_table = block_table;
   p.pairs = static_cast<const PairDesc*>(tile_area);
@@ -742,8 +908,28 @@ int prefill_tc(void* out, const void* q, const void* k_pool, const void* v_pool,
     return cuda_status(cudaGetLastError());
   };
   static uint64_t done_f16 = 0, done_bf16 = 0;  // racing first calls at worst set the attribute twice
-  if (layout->dtype == KPX_F16) return launch(prefill_tc_kernel<__half>, &done_f16);
-  return launch(prefill_tc_kernel<__nv_bfloat16>, &done_bf16);
+  const int rc = layout->dtype == KPX_F16 ? launch(prefill_tc_kernel<__half>, &done_f16)
+                                          : launch(prefill_tc_kernel<__nv_bfloat16>, &done_bf16);
+  if (rc != KPX_OK || merges.empty()) return rc;
+  const MergeDesc* md = reinterpret_cast<const MergeDesc*>(area + pair_bytes);
+  if (layout->dtype == KPX_F16)
+    prefill_merge_kernel<__half><<<dim3(unsigned(merges.size()), kTile / kMergeRowsPerCta), dim3(kD, kMergeRowLanes), 0, stream>>>(static_cast<__half*>(out), p.partials, md, num_q_heads);
+  else
+    prefill_merge_kernel<__nv_bfloat16><<<dim3(unsigned(merges.size()), kTile / kMergeRowsPerCta), dim3(kD, kMergeRowLanes), 0, stream>>>(static_cast<__nv_bfloat16*>(out), p.partials, md, num_q_heads);
+  return cuda_status(cudaGetLastError());
+}
+
+// Bytes of the work area prefill_tc may need for a call with total_q query tokens.
+int64_t prefill_tc_area_bytes(int32_t total_q, int32_t num_q_heads) {
+  const int64_t h = num_q_heads > 0 ? num_q_heads : 1;
+  // at most one pair entry per (128-row tile, head) and never more tiles than tokens, plus the
+  // parts of a cut last wave; one merge entry per cut item; the part slots
+  return align256((int64_t(total_q) + 1) * h * int64_t(sizeof(PairDesc)) + int64_t(kMaxPartSlots) * sizeof(PairDesc)) +
+         align256(int64_t(2) * kMaxPartSlots * sizeof(MergeDesc)) +
+         int64_t(kMaxPartSlots) * kPartSlotFloats * int64_t(sizeof(float));
 }
 
 }  // namespace kpx
+
+// Test knob (not in the public header): see g_prefill_split.
+extern "C" __attribute__((visibility("default"))) void kpx_internal_set_prefill_split(int v) { kpx::g_prefill_split = v; }

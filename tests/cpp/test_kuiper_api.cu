@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "base/paged_kv.h"
+#include "model/kv_cache_view.h"
 #include "op/batched_rope.h"
 #include "op/flash_attention.h"
 #include "op/kv_cache.h"
@@ -138,6 +139,16 @@ static void test_config1_fp32_layers() {
   EXPECT(bool(gp.forward(dpos.ptr<int32_t>(), H, layer, S, kv_dim, H / HKV, D, dout2, dq, dscore, dkc, dvc)));
   cudaStreamSynchronize(cfg->stream);
   EXPECT(max_abs_diff(to_host<float>(dout2), out_ref) < 1e-5f);
+  // the eager path's "slot mapping": views aliasing cache[layer][pos] (Model::slice_kv_cache)
+  auto views = model::slice_kv_cache(dkc, dvc, layer, pos, S, kv_dim);
+  EXPECT(views.first.size() == size_t(kv_dim) && views.second.size() == size_t(kv_dim));
+  EXPECT(views.first.ptr<float>() == dkc.ptr<float>() + (size_t(layer) * S + pos) * kv_dim);
+  EXPECT(views.first.device_type() == DeviceType::kDeviceCUDA);
+  EXPECT(to_host<float>(views.first) == k_ref);   // the row the store layer wrote
+  EXPECT(to_host<float>(views.second) == v);
+  const int32_t row[3] = {7, 2, -1};
+  EXPECT(model::paged_slot(row, 3, 16, 0) == 7 * 16 && model::paged_slot(row, 3, 16, 17) == 2 * 16 + 1);
+  EXPECT(model::paged_slot(row, 3, 16, 40) == -1 && model::paged_slot(row, 3, 16, 48) == -1);
 }
 
 // fp16 decode through FlashAttentionDecodeLayer (host pos and device pos) + CopyToKVCacheLayer.

@@ -51,21 +51,35 @@ def _run_chunked(oracle, dtype, q_heads, kv_heads, prompt_lens, chunk, seed=0, a
         nbytes = capi.prefill_workspace_bytes(int(cu[-1]), q_heads, kv_heads, D)
         ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
         capi.workspace_init(ws, nbytes)
-        capi.paged_prefill(out, dq, kp, vp, lay, torch.from_numpy(table).cuda(), max_blocks, cu, sp,
-                           len(active), q_heads, 1.0 / np.sqrt(D), ws, nbytes)
-        assert capi.workspace_status(ws) == 0
-        got = kvtest.storage_to_f32(kvtest.from_device(out, dtype), dtype)
         # oracle: gather each sequence to the reference's contiguous layout, causal MHA
+        refs = []
         for i, (b, n_b) in enumerate(zip(active, n)):
             length = start[b] + n_b
             kc = kvtest.storage_to_f32(oracle.gather_paged(kp_ref, table[i], length, kv_heads, D, BS), dtype)
             vc = kvtest.storage_to_f32(oracle.gather_paged(vp_ref, table[i], length, kv_heads, D, BS), dtype)
-            ref = oracle.mha_prefill(start[b], kvtest.storage_to_f32(q_rows[cu[i]:cu[i + 1]], dtype), q_heads,
-                                     length, kv_dim, q_heads // kv_heads, D, kc.reshape(-1), vc.reshape(-1),
-                                     threads=oracle.max_threads())
-            e = kvtest.assert_attention_close(got[cu[i]:cu[i + 1]], ref,
-                                              f"prefill {dtype} seq {b} start {start[b]} {atol_note}", dtype)
-            worst = (max(worst[0], e[0]), max(worst[1], e[1]))
+            refs.append(oracle.mha_prefill(start[b], kvtest.storage_to_f32(q_rows[cu[i]:cu[i + 1]], dtype), q_heads,
+                                           length, kv_dim, q_heads // kv_heads, D, kc.reshape(-1), vc.reshape(-1),
+                                           threads=oracle.max_threads()))
+        # tensor-core tiles with the key range whole / cut in 2 / cut in 4 parts and merged / cut by
+        # the library's own rule, and the per-query streaming path: each against the oracle
+        d_table = torch.from_numpy(table).cuda()
+        for path, split in ((0, 0), (0, 2), (0, 4), (0, -1), (1, -1)):
+            if dtype == "f32" and (path, split) != (0, -1):
+                continue  # fp32 pools always take the streaming path
+            capi.lib().kpx_internal_set_prefill_path(path)
+            capi.lib().kpx_internal_set_prefill_split(split)
+            out.fill_(float("nan"))
+            capi.paged_prefill(out, dq, kp, vp, lay, d_table, max_blocks, cu, sp, len(active), q_heads,
+                               1.0 / np.sqrt(D), ws, nbytes)
+            assert capi.workspace_status(ws) == 0
+            got = kvtest.storage_to_f32(kvtest.from_device(out, dtype), dtype)
+            for i, b in enumerate(active):
+                e = kvtest.assert_attention_close(
+                    got[cu[i]:cu[i + 1]], refs[i],
+                    f"prefill {dtype} path {path} split {split} seq {b} start {start[b]} {atol_note}", dtype)
+                worst = (max(worst[0], e[0]), max(worst[1], e[1]))
+        capi.lib().kpx_internal_set_prefill_path(0)
+        capi.lib().kpx_internal_set_prefill_split(-1)
         for b, n_b in zip(active, n):
             start[b] += n_b
     # cache contents after all chunks: bit-exact
