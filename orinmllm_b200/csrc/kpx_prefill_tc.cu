@@ -12,6 +12,9 @@
 //                running maximum moved lazily, O_x rescaled in tensor memory when it moves
 // The MMA order  PV_0(j) QK_0(j+1) | PV_1(j) QK_1(j+1)  keeps the tensor core on one item while
 // the softmax threads work on the other.
+// A CTA may own only a range of its pair's key tiles (a call with too few pairs to fill the SMs
+// is cut that way): it then leaves unnormalised rows with their maximum and sum in a slot of the
+// work area, and prefill_merge_kernel combines the parts.
 // Every mbarrier wait is bounded; a role that gives up raises a CTA-wide flag that ends the
 // other roles' waits, TMEM is freed on every path and the workspace status word is raised.
 #include <cuda.h>  // CUtensorMap and the enums of cuTensorMapEncodeTiled (types only; no libcuda link)
