@@ -382,32 +382,47 @@ __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t 
   tmem_wait_st();
 }
 
-// out rows of one item = O / l.  Called by the 256 softmax threads of the item (contains their barrier).
+// out rows of one item = O / l.  Called by the 256 softmax threads of the item (contains their
+// barrier).  A thread holds 128 contiguous bytes of one row, so a warp's direct stores would hit
+// 32 different rows; the rows go through `stage` (32 KB of shared memory nobody else touches any
+// more: the item's Q tile) and leave as whole 256-byte rows, 16 lanes each.
 template <typename T>
 __device__ __forceinline__ void write_item(uint32_t tO, uint32_t lane_addr, int row, int half, const ItemDesc& it,
-                                           int num_q_heads, void* out, float* s_half, int bar_id, const RowState& st) {
+                                           int num_q_heads, void* out, float* s_half, int bar_id, const RowState& st,
+                                           uint8_t* stage) {
   const float l_mine = st.l.x + st.l.y;
   softmax_sync(bar_id);  // earlier readers of the exchange area are done
   s_half[half * kTile + row] = l_mine;
   softmax_sync(bar_id);
   const float l_row = l_mine + s_half[(half ^ 1) * kTile + row];
   const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-  uint8_t* orow = static_cast<uint8_t*>(out) + (int64_t(it.row0 + row) * num_q_heads + it.head) * (kD * 2) + half * 128;
   uint32_t r[32];
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
     tmem_ld32(tO + lane_addr + c * 32, r);
-    if (row < it.nrows) {
 #pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        uint4 w;
-        w.x = pack2<T>(__uint_as_float(r[8 * v + 0]) * inv, __uint_as_float(r[8 * v + 1]) * inv);
-        w.y = pack2<T>(__uint_as_float(r[8 * v + 2]) * inv, __uint_as_float(r[8 * v + 3]) * inv);
-        w.z = pack2<T>(__uint_as_float(r[8 * v + 4]) * inv, __uint_as_float(r[8 * v + 5]) * inv);
-        w.w = pack2<T>(__uint_as_float(r[8 * v + 6]) * inv, __uint_as_float(r[8 * v + 7]) * inv);
-        *reinterpret_cast<uint4*>(orow + (c * 4 + v) * 16) = w;
-      }
+    for (int v = 0; v < 4; ++v) {
+      uint4 w;
+      w.x = pack2<T>(__uint_as_float(r[8 * v + 0]) * inv, __uint_as_float(r[8 * v + 1]) * inv);
+      w.y = pack2<T>(__uint_as_float(r[8 * v + 2]) * inv, __uint_as_float(r[8 * v + 3]) * inv);
+      w.z = pack2<T>(__uint_as_float(r[8 * v + 4]) * inv, __uint_as_float(r[8 * v + 5]) * inv);
+      w.w = pack2<T>(__uint_as_float(r[8 * v + 6]) * inv, __uint_as_float(r[8 * v + 7]) * inv);
+      // 16-byte chunk (half*8 + c*4 + v) of the row, stored at a position rotated by the row so
+      // that the 32 rows of a warp spread over the banks
+      const int chunk = half * 8 + c * 4 + v;
+      *reinterpret_cast<uint4*>(stage + row * 256 + ((chunk ^ (row & 15)) << 4)) = w;
     }
+  }
+  softmax_sync(bar_id);  // the whole tile is staged
+  const int t = half * kTile + row;  // 0..255 within the item's threads
+  const int chunk = t & 15;
+  uint8_t* obase = static_cast<uint8_t*>(out) + (int64_t(it.row0) * num_q_heads + it.head) * (kD * 2) + chunk * 16;
+#pragma unroll
+  for (int i = 0; i < kTile / 16; ++i) {
+    const int rr = (t >> 4) + 16 * i;
+    if (rr < it.nrows)
+      *reinterpret_cast<uint4*>(obase + int64_t(rr) * num_q_heads * (kD * 2)) =
+          *reinterpret_cast<const uint4*>(stage + rr * 256 + ((chunk ^ (rr & 15)) << 4));
   }
 }
 
@@ -704,7 +719,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (!failed && wait_all(o_full + x, 0)) {
         if (pd.part < 0)
-          write_item<T>(tO, lane_addr, row, half, it, p.num_q_heads, p.out, my_half, bar_id, st);
+          write_item<T>(tO, lane_addr, row, half, it, p.num_q_heads, p.out, my_half, bar_id, st, sQ + x * kOperandB);
         else
           write_partial(tO, lane_addr, row, half, p.partials + pd.part * kPartSlotFloats + x * kPartItemFloats,
                         my_half, bar_id, st);
