@@ -1,4 +1,4 @@
-"""BASELINE configs[4](b): one 131072-token sequence at the Qwen3-8B attention shape sharded by
+"""BASELINE.json configs[4](b): one 131072-token sequence at the Qwen3-8B attention shape sharded by
 KV head over the ranks (8 KV heads -> 8/G per GPU), NCCL all-gather of the per-head outputs.
 Reports, per layer-step, the decode kernel time (max over ranks), its KV GB/s per GPU, and the
 all-gather latency separately.  Run with 1 process or under torchrun:
