@@ -102,3 +102,38 @@ def test_prefill_config3_shape_reduced(native_libs, oracle):
     # 2 sequences of 1024 tokens so the CPU oracle finishes in seconds
     worst = _run_chunked(oracle, "bf16", 28, 4, [1024, 1024], chunk=512, seed=5)
     print("config-3 (reduced) prefill parity: max_abs=%.3e max_rel=%.3e" % worst)
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_prefill_reference_cache_layout(native_libs, oracle, dtype):
+    """The reference's token-major cache [seq_len][kv_dim] (16-bit) through the tensor-core path:
+    the TMA tensor maps take the layout's strides, the block table is the identity, and a chunk
+    that starts inside a block and ends inside another is handled (start 40, 300 queries)."""
+    import torch
+    from orinmllm_b200 import capi
+    H, HKV, D, S = 12, 2, 128, 512
+    start, n = 40, 300
+    rng = np.random.default_rng(17)
+    kv_dim = HKV * D
+    kc = kvtest.to_storage(rng.standard_normal((S, kv_dim)).astype(np.float32), dtype)
+    vc = kvtest.to_storage(rng.standard_normal((S, kv_dim)).astype(np.float32), dtype)
+    q = kvtest.to_storage(rng.standard_normal((n, H * D)).astype(np.float32), dtype)
+    lay = capi.layout_contiguous(capi.dtype_code(kvtest.torch_dtype(dtype)), HKV, D, 16, S // 16)
+    table = torch.arange(S // 16, dtype=torch.int32, device="cuda")[None, :].contiguous()
+    dq, dk, dv = kvtest.to_device(q, dtype), kvtest.to_device(kc, dtype), kvtest.to_device(vc, dtype)
+    out = torch.full_like(dq, float("nan"))
+    nbytes = capi.prefill_workspace_bytes(n, H, HKV, D)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    capi.workspace_init(ws, nbytes)
+    ref = oracle.mha_prefill(start, kvtest.storage_to_f32(q, dtype), H, S, kv_dim, H // HKV, D,
+                             kvtest.storage_to_f32(kc, dtype).reshape(-1), kvtest.storage_to_f32(vc, dtype).reshape(-1),
+                             threads=oracle.max_threads())
+    for path in (0, 1):
+        capi.lib().kpx_internal_set_prefill_path(path)
+        out.fill_(float("nan"))
+        capi.paged_prefill(out, dq, dk, dv, lay, table, S // 16, np.array([0, n], np.int32),
+                           np.array([start], np.int32), 1, H, 1.0 / np.sqrt(D), ws, nbytes)
+        assert capi.workspace_status(ws) == 0
+        got = kvtest.storage_to_f32(kvtest.from_device(out, dtype), dtype)
+        kvtest.assert_attention_close(got, ref, f"prefill reference layout {dtype} path {path}", dtype)
+    capi.lib().kpx_internal_set_prefill_path(0)
