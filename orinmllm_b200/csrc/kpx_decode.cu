@@ -8,7 +8,9 @@
 // number of bytes whatever the spread of sequence lengths.  A warp that covers an
 // item completely writes its output directly; an item cut by a range boundary
 // leaves one partial (running max, sum, un-normalised accumulator) per warp in the
-// workspace, and a small second kernel merges the partials.
+// workspace, and the warp that delivers the item's last piece (an atomic counter per item,
+// nobody waits) assembles the output; an item cut into very many pieces (one very long
+// sequence) is assembled in two levels, 16 warps' pieces at a time.  One launch.
 //
 // Each warp is its own producer and consumer: it owns two K and two V tile slots in
 // shared memory, fetches the (block, kv head) tiles of its range through the block
