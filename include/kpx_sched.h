@@ -33,6 +33,14 @@ KPX_API void kpx_sched_destroy(kpx_sched* s);
  * also_register tokens are registered as a prefix of their own too (a shared system prompt). */
 KPX_API int32_t kpx_sched_submit(kpx_sched* s, const int32_t* prompt, int32_t prompt_len, int32_t max_new_tokens,
                                  int32_t also_register);
+/* One turn of a conversation (the reference's end-of-turn fix-up, demo/inference_common.h:
+ * 1334-1358): when generation ends, the last sampled token and the suffix_len >= 0 tokens the
+ * chat template puts after it are prefilled as well (rows with completes == 0, nothing is
+ * sampled), and the whole history is registered, so that the next turn's prompt hits all of it.
+ * The request is in state 4 (gap fill) meanwhile. */
+KPX_API int32_t kpx_sched_submit_turn(kpx_sched* s, const int32_t* prompt, int32_t prompt_len,
+                                      int32_t max_new_tokens, int32_t also_register,
+                                      const int32_t* turn_suffix, int32_t suffix_len);
 /* -> number of requests moved from waiting to running. */
 KPX_API int32_t kpx_sched_admit(kpx_sched* s);
 
@@ -55,16 +63,17 @@ KPX_API int kpx_sched_decode_arrays(const kpx_sched* s, int32_t* request_ids, in
                                     int32_t* block_table, int32_t max_blocks);
 KPX_API int kpx_sched_complete_decode(kpx_sched* s, const int32_t* sampled, int32_t rows);
 
-/* Requests.  state: 0 waiting, 1 prefill, 2 decode, 3 finished (also: unknown id). */
+/* Requests.  state: 0 waiting, 1 prefill, 2 decode, 3 finished (also: unknown id), 4 gap fill. */
 KPX_API int32_t kpx_sched_state(const kpx_sched* s, int32_t request);
 KPX_API int32_t kpx_sched_reused_tokens(const kpx_sched* s, int32_t request);
-/* prompt followed by the generated tokens; -> their number (copies at most cap of them) */
+/* prompt followed by the generated tokens (then the turn's suffix, once the turn has ended);
+ * -> their number (copies at most cap of them) */
 KPX_API int32_t kpx_sched_tokens(const kpx_sched* s, int32_t request, int32_t* out, int32_t cap);
 KPX_API int kpx_sched_forget(kpx_sched* s, int32_t request);
 KPX_API int32_t kpx_sched_num_waiting(const kpx_sched* s);
 KPX_API int32_t kpx_sched_num_running(const kpx_sched* s);
 /* out[0..11] = submitted, admitted, finished, prompt_tokens, reused_tokens, prefilled_tokens,
- * decoded_tokens, prefill_steps, decode_steps, admission_stalls, peak_blocks_in_use, 0 */
+ * decoded_tokens, prefill_steps, decode_steps, admission_stalls, peak_blocks_in_use, gap_tokens */
 KPX_API int kpx_sched_stats(const kpx_sched* s, int64_t* out12);
 
 #ifdef __cplusplus

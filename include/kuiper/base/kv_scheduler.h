@@ -4,7 +4,13 @@
 // Per request it follows the order of operations of the reference's generate_response
 // (demo/inference_common.h:1050-1262) and PrefixCacheManager (:757-853):
 //     match (adds a reference)  ->  prefill from the matched position, in chunks  ->
-//     one decode step per generated token  ->  register the sequence  ->  release the match.
+//     one decode step per generated token  ->  (fill the gap)  ->  register the sequence  ->
+//     release the match.
+// "Fill the gap" is the reference's end-of-turn fix-up (demo/inference_common.h:1334-1358): the
+// last sampled token (the end marker) was never fed in, and the chat template appends
+// separator tokens after it, so the history that the next turn will present is longer than
+// what the cache holds; the missing tokens are prefilled, without sampling, before the
+// whole history is registered.  A request asks for it with submit_turn().
 // The reference runs one request at a time on a contiguous cache; here requests run
 // concurrently on the block pool: a hit maps the matched blocks by reference, a sequence that
 // appends into a shared, partly filled block first gets a private copy (copy-on-write, logged
@@ -14,8 +20,8 @@
 // Differences from the reference, on purpose:
 //   * a full hit still recomputes the last prompt token, so that there is an attention output
 //     to sample from (the reference skips prefill and reads a stale logits buffer);
-//   * the registered sequence is cut to the tokens whose K/V are in the cache (the last
-//     sampled token has none yet).
+//   * without the gap fill, the registered sequence is cut to the tokens whose K/V are in the
+//     cache (the last sampled token has none yet).
 #ifndef KUIPER_INCLUDE_BASE_KV_SCHEDULER_H_
 #define KUIPER_INCLUDE_BASE_KV_SCHEDULER_H_
 
@@ -39,7 +45,7 @@ struct KVSchedulerConfig {
   bool use_prefix_cache = true;
 };
 
-enum class RequestState : int32_t { kWaiting = 0, kPrefill = 1, kDecode = 2, kFinished = 3 };
+enum class RequestState : int32_t { kWaiting = 0, kPrefill = 1, kDecode = 2, kFinished = 3, kGapFill = 4 };
 
 // Inputs of one kpx_rope_append / kpx_append + kpx_paged_prefill call sequence.
 struct PrefillStep {
@@ -67,6 +73,7 @@ struct DecodeStep {
 struct KVSchedulerStats {
   int64_t submitted = 0, admitted = 0, finished = 0;
   int64_t prompt_tokens = 0, reused_tokens = 0, prefilled_tokens = 0, decoded_tokens = 0;
+  int64_t gap_tokens = 0;              // end-of-turn tokens prefilled without sampling
   int64_t prefill_steps = 0, decode_steps = 0;
   int64_t admission_stalls = 0;        // admit() calls that left a request waiting for blocks
   int32_t peak_blocks_in_use = 0;
@@ -101,6 +108,19 @@ class KVScheduler {
     return id;
   }
 
+  // A request that is one turn of a conversation: when generation ends, the last sampled token
+  // and `turn_suffix` (the template's separators after it; may be empty) are prefilled too, so
+  // that the registered sequence is the whole history the next turn starts with.
+  int32_t submit_turn(const std::vector<int32_t>& prompt, int32_t max_new_tokens,
+                      const std::vector<int32_t>& turn_suffix, int32_t also_register = 0) {
+    const int32_t id = submit(prompt, max_new_tokens, also_register);
+    if (id < 0) return id;
+    Request& r = requests_[id];
+    r.fill_gap = true;
+    r.turn_suffix = turn_suffix;
+    return id;
+  }
+
   // Moves waiting requests into the running set, first come first served, while the pool can
   // hold each one to its last token.  Returns how many were admitted.
   int32_t admit() {
@@ -127,9 +147,12 @@ class KVScheduler {
     int32_t budget = config_.max_prefill_tokens;
     for (int32_t id : running_) {
       Request& r = requests_[id];
-      if (r.state != RequestState::kPrefill) continue;
+      if (r.state != RequestState::kPrefill && r.state != RequestState::kGapFill) continue;
       if (budget <= 0 || step->num_rows() >= config_.max_prefill_rows) break;
-      const int32_t n = std::min({config_.prefill_chunk, r.prompt_len - r.computed, budget});
+      const bool gap = r.state == RequestState::kGapFill;
+      const int32_t target = gap ? static_cast<int32_t>(r.tokens.size()) : r.prompt_len;
+      const int32_t n = std::min({config_.prefill_chunk, target - r.computed, budget});
+      if (n <= 0) continue;
       std::vector<int64_t> slots;
       if (!pool_->append(r.seq, n, &slots)) continue;  // cannot happen after admission; skip, never corrupt
       step->request_ids.push_back(id);
@@ -141,9 +164,10 @@ class KVScheduler {
       }
       step->cu_q_lens.push_back(step->num_tokens());
       r.computed += n;
-      step->completes.push_back(r.computed == r.prompt_len ? 1 : 0);
+      step->completes.push_back(!gap && r.computed == r.prompt_len ? 1 : 0);
       budget -= n;
       stats_.prefilled_tokens += n;
+      if (gap) stats_.gap_tokens += n;
     }
     note_usage();
     if (step->num_rows() == 0) return false;
@@ -155,8 +179,11 @@ class KVScheduler {
   // entries of rows that did not complete are ignored).
   void complete_prefill(const PrefillStep& step, const std::vector<int32_t>& sampled) {
     for (int32_t i = 0; i < step.num_rows(); ++i) {
-      if (!step.completes[static_cast<size_t>(i)]) continue;
       Request& r = requests_[step.request_ids[static_cast<size_t>(i)]];
+      // a gap row whose history is now cached in full is done (nothing is sampled from it)
+      if (r.state == RequestState::kGapFill && r.computed == static_cast<int32_t>(r.tokens.size()))
+        r.state = RequestState::kFinished;
+      if (!step.completes[static_cast<size_t>(i)]) continue;
       r.state = RequestState::kDecode;
       push_token(step.request_ids[static_cast<size_t>(i)], r, sampled[static_cast<size_t>(i)]);
     }
@@ -226,7 +253,7 @@ class KVScheduler {
     auto it = requests_.find(id);
     return it == requests_.end() ? -1 : it->second.reused;
   }
-  // prompt followed by the tokens generated so far
+  // prompt followed by the tokens generated so far (and, once a turn has ended, its suffix)
   const std::vector<int32_t>* tokens(int32_t id) const {
     auto it = requests_.find(id);
     return it == requests_.end() ? nullptr : &it->second.tokens;
@@ -249,6 +276,8 @@ class KVScheduler {
     int32_t computed = 0;         // tokens whose K/V are in the cache
     int32_t reserved = 0;         // blocks this request may still take from the free list
     int32_t also_register = 0;    // extra prefix length to register at the end
+    bool fill_gap = false;        // prefill the end-of-turn tokens before registering
+    std::vector<int32_t> turn_suffix;
     std::vector<int32_t> matched_prefix;
     RequestState state = RequestState::kWaiting;
   };
@@ -256,6 +285,12 @@ class KVScheduler {
   int32_t blocks_for(int32_t tokens) const {
     const int32_t bs = pool_->config().block_size;
     return (tokens + bs - 1) / bs;
+  }
+  // Most tokens the request will ever have in the cache: the last sampled token is cached only
+  // by the gap fill, which also adds the turn's suffix.
+  static int32_t final_len(const Request& r) {
+    const int32_t n = r.prompt_len + r.max_new - 1;
+    return r.fill_gap ? n + 1 + static_cast<int32_t>(r.turn_suffix.size()) : n;
   }
 
   bool try_admit(int32_t id) {
@@ -282,9 +317,8 @@ class KVScheduler {
     // blocks of its final length minus the mapped ones, plus one if the first append lands in
     // a shared, partly filled block (copy-on-write).
     const int32_t bs = pool_->config().block_size;
-    const int32_t final_len = r.prompt_len + r.max_new - 1;  // the last sampled token is never cached
     const int32_t mapped = blocks_for(reused);
-    const int32_t need = blocks_for(final_len) - mapped + ((reused % bs) != 0 ? 1 : 0);
+    const int32_t need = blocks_for(final_len(r)) - mapped + ((reused % bs) != 0 ? 1 : 0);
     int32_t avail = pool_->num_free() - reserved_total_;
     if (need > avail && config_.use_prefix_cache && cache_) {
       // spans nobody references can make room (oldest first)
@@ -311,7 +345,14 @@ class KVScheduler {
     (void)id;
     r.tokens.push_back(token);
     const int32_t generated = static_cast<int32_t>(r.tokens.size()) - r.prompt_len;
-    if (generated >= r.max_new || (is_end_ && is_end_(token))) r.state = RequestState::kFinished;
+    if (generated >= r.max_new || (is_end_ && is_end_(token))) {
+      if (r.fill_gap) {
+        r.tokens.insert(r.tokens.end(), r.turn_suffix.begin(), r.turn_suffix.end());
+        r.state = RequestState::kGapFill;
+      } else {
+        r.state = RequestState::kFinished;
+      }
+    }
   }
 
   // Finished requests: register what is cached, release the match, give the sequence back.
@@ -352,10 +393,9 @@ class KVScheduler {
       if (r.seq < 0) continue;
       const std::vector<int32_t>* b = pool_->blocks(r.seq);
       const int32_t have = b ? static_cast<int32_t>(b->size()) : 0;
-      const int32_t final_len = r.prompt_len + r.max_new - 1;
       // a copy-on-write still ahead: the sequence has not appended yet and its last block is shared and partial
       const bool cow_ahead = (r.computed == r.reused) && (r.reused % bs) != 0;
-      r.reserved = std::max(0, blocks_for(final_len) - have) + (cow_ahead ? 1 : 0);
+      r.reserved = std::max(0, blocks_for(final_len(r)) - have) + (cow_ahead ? 1 : 0);
       reserve += r.reserved;
     }
     reserved_total_ = reserve;

@@ -44,6 +44,13 @@ extern "C" int32_t kpx_sched_submit(kpx_sched* s, const int32_t* prompt, int32_t
   if (!s || !prompt || prompt_len <= 0) return -1;
   return s->sched->submit(std::vector<int32_t>(prompt, prompt + prompt_len), max_new_tokens, also_register);
 }
+extern "C" int32_t kpx_sched_submit_turn(kpx_sched* s, const int32_t* prompt, int32_t prompt_len,
+                                         int32_t max_new_tokens, int32_t also_register,
+                                         const int32_t* turn_suffix, int32_t suffix_len) {
+  if (!s || !prompt || prompt_len <= 0 || suffix_len < 0 || (suffix_len > 0 && !turn_suffix)) return -1;
+  return s->sched->submit_turn(std::vector<int32_t>(prompt, prompt + prompt_len), max_new_tokens,
+                               std::vector<int32_t>(turn_suffix, turn_suffix + suffix_len), also_register);
+}
 extern "C" int32_t kpx_sched_admit(kpx_sched* s) { return s ? s->sched->admit() : -1; }
 
 extern "C" int kpx_sched_next_prefill(kpx_sched* s) { return (s && s->sched->next_prefill(&s->prefill)) ? 1 : 0; }
@@ -130,7 +137,7 @@ extern "C" int kpx_sched_stats(const kpx_sched* s, int64_t* out12) {
   const base::KVSchedulerStats& st = s->sched->stats();
   const int64_t v[12] = {st.submitted, st.admitted, st.finished, st.prompt_tokens, st.reused_tokens,
                          st.prefilled_tokens, st.decoded_tokens, st.prefill_steps, st.decode_steps,
-                         st.admission_stalls, st.peak_blocks_in_use, 0};
+                         st.admission_stalls, st.peak_blocks_in_use, st.gap_tokens};
   std::memcpy(out12, v, sizeof(v));
   return KPX_OK;
 }

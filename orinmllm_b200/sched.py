@@ -16,6 +16,7 @@ SIGNATURES = {
     "kpx_sched_create": (_P, [_P, _I32, _I32, _I32, _I32, _I32]),
     "kpx_sched_destroy": (None, [_P]),
     "kpx_sched_submit": (_I32, [_P, _P, _I32, _I32, _I32]),
+    "kpx_sched_submit_turn": (_I32, [_P, _P, _I32, _I32, _I32, _P, _I32]),
     "kpx_sched_admit": (_I32, [_P]),
     "kpx_sched_next_prefill": (C.c_int, [_P]),
     "kpx_sched_prefill_shape": (C.c_int, [_P, _P, _P, _P]),
@@ -35,7 +36,8 @@ SIGNATURES = {
 }
 
 STATS_FIELDS = ("submitted", "admitted", "finished", "prompt_tokens", "reused_tokens", "prefilled_tokens",
-                "decoded_tokens", "prefill_steps", "decode_steps", "admission_stalls", "peak_blocks_in_use")
+                "decoded_tokens", "prefill_steps", "decode_steps", "admission_stalls", "peak_blocks_in_use",
+                "gap_tokens")
 
 _bound = False
 
@@ -104,6 +106,17 @@ class Scheduler:
         rid = lib().kpx_sched_submit(self._h, _ptr(p), len(p), max_new_tokens, also_register)
         if rid < 0:
             raise ValueError("kpx_sched_submit refused the request")
+        return rid
+
+    def submit_turn(self, prompt, max_new_tokens, turn_suffix=(), also_register=0) -> int:
+        """One turn of a conversation: at its end the last sampled token and `turn_suffix` are
+        prefilled too and the whole history is registered (kpx_sched_submit_turn)."""
+        p = np.ascontiguousarray(prompt, dtype=np.int32)
+        sfx = np.ascontiguousarray(turn_suffix, dtype=np.int32)
+        rid = lib().kpx_sched_submit_turn(self._h, _ptr(p), len(p), max_new_tokens, also_register,
+                                          _ptr(sfx) if len(sfx) else None, len(sfx))
+        if rid < 0:
+            raise ValueError("kpx_sched_submit_turn refused the request")
         return rid
 
     def admit(self) -> int:
@@ -179,4 +192,4 @@ class Scheduler:
     def stats(self) -> dict:
         out = np.zeros(12, np.int64)
         lib().kpx_sched_stats(self._h, _ptr(out))
-        return dict(zip(STATS_FIELDS, (int(v) for v in out[:11])))
+        return dict(zip(STATS_FIELDS, (int(v) for v in out[:12])))

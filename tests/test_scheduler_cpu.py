@@ -154,3 +154,65 @@ def test_shared_prompt_workload_block_count():
     # request 0 keeps its 16 suffix blocks in the tree; the 255 followers ran together
     assert st["peak_blocks_in_use"] == prefix // BS + suffix // BS + (n_req - 1) * per_request
     assert m.cow_events == 0
+
+
+def test_turn_end_gap_fill_registers_the_whole_history():
+    """The end-of-turn fix-up of the reference (demo/inference_common.h:1334-1358): the last
+    sampled token and the template's separators are prefilled without sampling, the whole
+    history is registered, and the next turn's prompt reuses all of it."""
+    m = kvm.KvManager(256, BS, seed=4)
+    s = sched.Scheduler(m, prefill_chunk=8)
+    prompt = np.arange(1000, 1037, dtype=np.int32)
+    suffix = np.array([198, 199], np.int32)
+    gap_rows = []
+
+    def prefill_hook(p):
+        for i, rid in enumerate(p.request_ids):
+            if s.state(int(rid)) == 4:
+                a, b = p.cu_q_lens[i], p.cu_q_lens[i + 1]
+                gap_rows.append((list(p.positions[a:b]), list(p.token_ids[a:b]), int(p.completes[i])))
+                check_slots(p.positions[a:b], p.slot_mapping[a:b], p.block_table[i])
+
+    t1 = s.submit_turn(prompt, 5, suffix)
+    drive(s, sample=lambda rid, step: 500 + step, prefill_hook=prefill_hook)
+    hist = s.tokens(t1)
+    assert len(hist) == len(prompt) + 5 + len(suffix) and list(hist[-2:]) == [198, 199]
+    # the gap: the last sampled token, then the suffix, at the positions after the cached ones; never sampled from
+    n_cached = len(prompt) + 4
+    assert [x for r in gap_rows for x in r[0]] == list(range(n_cached, n_cached + 3))
+    assert [x for r in gap_rows for x in r[1]] == list(hist[n_cached:])
+    assert all(r[2] == 0 for r in gap_rows)
+    st = s.stats()
+    assert st["gap_tokens"] == 3 and st["prefilled_tokens"] == len(prompt) + 3 and st["finished"] == 1
+    assert m.num_free == 256 - (len(hist) + BS - 1) // BS  # only the registered span holds blocks
+    # next turn: history + a new message; everything cached is reused (whole blocks by reference,
+    # the partial last block copied on first write)
+    t2 = s.submit_turn(np.concatenate([hist, np.arange(2000, 2010, dtype=np.int32)]), 3, suffix)
+    drive(s, sample=lambda rid, step: 700 + step)
+    assert s.reused_tokens(t2) == len(hist)
+    assert m.cow_events == (1 if len(hist) % BS else 0)
+    # without the gap fill the registered span stops before the last sampled token
+    m2 = kvm.KvManager(256, BS, seed=4)
+    s2 = sched.Scheduler(m2, prefill_chunk=8)
+    u1 = s2.submit(prompt, 5)
+    drive(s2, sample=lambda rid, step: 500 + step)
+    h2 = s2.tokens(u1)
+    u2 = s2.submit(np.concatenate([h2, suffix, np.arange(2000, 2010, dtype=np.int32)]), 3)
+    drive(s2)
+    assert s2.reused_tokens(u2) == len(h2) - 1
+
+
+def test_gap_fill_blocks_are_reserved_at_admission():
+    """A turn whose gap crosses into new blocks cannot run the pool dry: the blocks of the last
+    sampled token and the suffix are part of the reservation."""
+    m = kvm.KvManager(8, BS, seed=1)
+    s = sched.Scheduler(m, use_prefix_cache=False)
+    suffix = np.arange(40, dtype=np.int32)                  # 3 more blocks at the end
+    a = s.submit_turn(np.arange(30, dtype=np.int32), 3, suffix)   # 30 + 3 + 40 = 73 tokens = 5 blocks
+    b = s.submit_turn(np.arange(30, dtype=np.int32), 3, suffix)   # does not fit beside a
+    s.admit()
+    assert s.state(a) == 1 and s.state(b) == 0
+    drive(s)
+    st = s.stats()
+    assert st["finished"] == 2 and st["admission_stalls"] > 0 and st["peak_blocks_in_use"] <= 8
+    assert st["gap_tokens"] == 2 * 41 and m.num_free == 8
