@@ -1,7 +1,7 @@
 // K/V append into the block pool, RoPE(+append), sin/cos tables, copy-on-write
 // block copy and block refcount updates.  All of these are pure data movement
-// (or element-wise fp32 math) bound by HBM bandwidth: 128-bit accesses, one
-// 16-byte vector per thread per step, grid-stride loops sized from the SM count.
+// (or element-wise fp32 math) bound by HBM bandwidth: 128-bit accesses,
+// grid-stride loops sized from the SM count.
 #include "kpx_common.cuh"
 
 namespace kpx {
@@ -31,31 +31,73 @@ __device__ __forceinline__ int64_t slot_head_offset_bytes(const LayoutDev& L, in
   return (blk * L.block_stride + int64_t(h) * L.head_stride + off * L.token_stride) * L.elt_bytes;
 }
 
-// One thread moves one 16-byte vector of K or V of one token.
-__global__ void append_kernel(uint8_t* __restrict__ k_pool, uint8_t* __restrict__ v_pool,
-                              const uint8_t* __restrict__ k_src, const uint8_t* __restrict__ v_src,
-                              const int64_t* __restrict__ slot_mapping,
-                              const int32_t* __restrict__ pos_dev, int32_t pos_bias,
-                              int32_t num_tokens, LayoutDev L) {
+// token index and remainder of work item i (32-bit division whenever the item count allows it)
+__device__ __forceinline__ void split_item(int64_t i, int per_tok, bool small, int64_t& t, int& r) {
+  if (small) {
+    const uint32_t q = uint32_t(i) / uint32_t(per_tok);
+    t = q;
+    r = int(uint32_t(i) - q * uint32_t(per_tok));
+  } else {
+    t = i / per_tok;
+    r = int(i - t * per_tok);
+  }
+}
+__device__ __forceinline__ int64_t slot_head_offset_bytes_fast(const LayoutDev& L, int64_t slot, int h) {
+  int64_t blk, off;
+  if (uint64_t(slot) < 0x80000000ull) {
+    const uint32_t b = uint32_t(slot) / uint32_t(L.block_size);
+    blk = b;
+    off = uint32_t(slot) - b * uint32_t(L.block_size);
+  } else {
+    blk = slot / L.block_size;
+    off = slot - blk * L.block_size;
+  }
+  return (blk * L.block_stride + int64_t(h) * L.head_stride + off * L.token_stride) * L.elt_bytes;
+}
+
+// One thread moves kAppendUnroll 16-byte vectors of K or V per step of the grid-stride loop:
+// all of a step's loads are issued before its first store, so that a thread keeps several
+// loads in flight (one at a time leaves about 32 KB per SM in flight, short of what the
+// memory system needs to run at full rate).
+constexpr int kAppendUnroll = 4;
+__global__ void __launch_bounds__(256)
+append_kernel(uint8_t* __restrict__ k_pool, uint8_t* __restrict__ v_pool,
+              const uint8_t* __restrict__ k_src, const uint8_t* __restrict__ v_src,
+              const int64_t* __restrict__ slot_mapping, const int32_t* __restrict__ pos_dev,
+              int32_t pos_bias, int32_t num_tokens, LayoutDev L) {
   const int vec_per_head = L.head_size * L.elt_bytes / 16;
   const int vec_per_tok = vec_per_head * L.num_kv_heads;
   const int which_n = v_pool ? 2 : 1;
-  const int64_t total = int64_t(num_tokens) * vec_per_tok * which_n;
+  const int per_tok = vec_per_tok * which_n;
+  const int64_t total = int64_t(num_tokens) * per_tok;
+  const bool small = total < (int64_t(1) << 31);
   int64_t base_slot = 0;
   if (!slot_mapping) base_slot = int64_t(pos_dev ? *pos_dev : 0) + pos_bias;
-  for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total;
-       i += int64_t(gridDim.x) * blockDim.x) {
-    int64_t t = i / (vec_per_tok * which_n);
-    int r = int(i - t * (vec_per_tok * which_n));
-    int which = r / vec_per_tok;
-    int vec = r - which * vec_per_tok;
-    int h = vec / vec_per_head;
-    int vi = vec - h * vec_per_head;
-    int64_t slot = slot_mapping ? slot_mapping[t] : base_slot + t;
-    if (slot < 0) continue;
-    const uint8_t* src = (which ? v_src : k_src) + (t * vec_per_tok + vec) * 16;
-    uint8_t* dst = (which ? v_pool : k_pool) + slot_head_offset_bytes(L, slot, h) + vi * 16;
-    *reinterpret_cast<uint4*>(dst) = __ldg(reinterpret_cast<const uint4*>(src));
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t i0 = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i0 < total; i0 += stride * kAppendUnroll) {
+    uint4 val[kAppendUnroll];
+    uint8_t* dst[kAppendUnroll];
+#pragma unroll
+    for (int u = 0; u < kAppendUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      dst[u] = nullptr;
+      if (i >= total) continue;
+      int64_t t;
+      int r;
+      split_item(i, per_tok, small, t, r);
+      const int which = r >= vec_per_tok ? 1 : 0;
+      const int vec = r - which * vec_per_tok;
+      const int h = vec / vec_per_head;
+      const int vi = vec - h * vec_per_head;
+      // the source row exists whatever the slot says: its load does not wait for the slot's
+      val[u] = __ldg(reinterpret_cast<const uint4*>((which ? v_src : k_src) + (t * vec_per_tok + vec) * 16));
+      const int64_t slot = slot_mapping ? slot_mapping[t] : base_slot + t;
+      if (slot < 0) continue;
+      dst[u] = (which ? v_pool : k_pool) + slot_head_offset_bytes_fast(L, slot, h) + vi * 16;
+    }
+#pragma unroll
+    for (int u = 0; u < kAppendUnroll; ++u)
+      if (dst[u]) *reinterpret_cast<uint4*>(dst[u]) = val[u];
   }
 }
 
@@ -149,6 +191,63 @@ __global__ void rope_append_kernel(T* __restrict__ q, T* __restrict__ k, const T
   }
 }
 
+// ---- token-walking form of the plain append ------------------------------------------
+// When a token's work items fit one CTA (<= 1024), thread r of the CTA does item r of every
+// token the CTA visits (tokens blockIdx.x, blockIdx.x + gridDim.x, ...).  A thread's role
+// (which head, which vector, K or V) is then fixed for the whole launch and is decoded once;
+// per token there is one slot fetch and one 64-bit base address.  append_kernel above (one flat
+// index per item, decoded anew each time) remains the fallback for wider tokens: it spends
+// about half of the SM's issue slots on index arithmetic at 16 bytes per item.  (The same
+// form of the RoPE kernel measured no faster than the flat one and is not kept.)
+__device__ __forceinline__ int64_t slot_base_bytes(const LayoutDev& L, int64_t slot) {
+  int64_t blk, off;
+  if (uint64_t(slot) < 0x80000000ull) {
+    const uint32_t b = uint32_t(slot) / uint32_t(L.block_size);
+    blk = b;
+    off = uint32_t(slot) - b * uint32_t(L.block_size);
+  } else {
+    blk = slot / L.block_size;
+    off = slot - blk * L.block_size;
+  }
+  return (blk * L.block_stride + off * L.token_stride) * L.elt_bytes;
+}
+
+constexpr int kTokenUnroll = 4;
+__global__ void __launch_bounds__(1024)
+append_token_kernel(uint8_t* __restrict__ k_pool, uint8_t* __restrict__ v_pool,
+                    const uint8_t* __restrict__ k_src, const uint8_t* __restrict__ v_src,
+                    const int64_t* __restrict__ slot_mapping, const int32_t* __restrict__ pos_dev,
+                    int32_t pos_bias, int32_t num_tokens, LayoutDev L) {
+  const int vec_per_head = L.head_size * L.elt_bytes / 16;
+  const int vec_per_tok = vec_per_head * L.num_kv_heads;
+  const int r = threadIdx.x;
+  if (r >= vec_per_tok * (v_pool ? 2 : 1)) return;
+  const int which = r >= vec_per_tok ? 1 : 0;
+  const int vec = r - which * vec_per_tok;
+  const int h = vec / vec_per_head;
+  const int vi = vec - h * vec_per_head;
+  const uint8_t* src = (which ? v_src : k_src) + vec * 16;
+  uint8_t* pool = (which ? v_pool : k_pool) + int64_t(h) * L.head_stride * L.elt_bytes + vi * 16;
+  const int64_t src_tok_bytes = int64_t(vec_per_tok) * 16;
+  int64_t base_slot = 0;
+  if (!slot_mapping) base_slot = int64_t(pos_dev ? *pos_dev : 0) + pos_bias;
+  for (int64_t t0 = blockIdx.x; t0 < num_tokens; t0 += int64_t(gridDim.x) * kTokenUnroll) {
+    uint4 val[kTokenUnroll];
+    int64_t slot[kTokenUnroll];
+#pragma unroll
+    for (int u = 0; u < kTokenUnroll; ++u) {
+      const int64_t t = t0 + int64_t(u) * gridDim.x;
+      slot[u] = -1;
+      if (t >= num_tokens) continue;
+      val[u] = __ldg(reinterpret_cast<const uint4*>(src + t * src_tok_bytes));
+      slot[u] = slot_mapping ? slot_mapping[t] : base_slot + t;
+    }
+#pragma unroll
+    for (int u = 0; u < kTokenUnroll; ++u)
+      if (slot[u] >= 0) *reinterpret_cast<uint4*>(pool + slot_base_bytes(L, slot[u])) = val[u];
+  }
+}
+
 __global__ void sin_cos_kernel(float* __restrict__ sin_cache, float* __restrict__ cos_cache,
                                int32_t head_size, int32_t max_seq_len, float theta) {
   int64_t total = int64_t(head_size) * max_seq_len;
@@ -234,6 +333,22 @@ inline int grid_for(int64_t work_items, int threads) {
   return int(blocks);
 }
 
+// Grid of a token-walking kernel: one CTA per token up to what the SMs hold at once (from the
+// occupancy calculator, looked up once per kernel and CTA size).
+template <typename Kernel>
+inline int token_grid(Kernel kernel, int64_t num_tokens, int threads) {
+  static int per_sm_cache[33] = {};  // index threads / 32; 0 = not looked up yet
+  int& per_sm = per_sm_cache[threads / 32];
+  if (per_sm == 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) n = 1;
+    per_sm = n;
+  }
+  const DeviceInfo& di = device_info();
+  const int64_t cap = int64_t(di.sm_count > 0 ? di.sm_count : 148) * per_sm;
+  return int(num_tokens < cap ? (num_tokens < 1 ? 1 : num_tokens) : cap);
+}
+
 }  // namespace
 }  // namespace kpx
 
@@ -249,8 +364,19 @@ extern "C" int kpx_append(void* k_pool, void* v_pool, const kpx_kv_layout* layou
   if (!device_info().ok) return KPX_ERR_CUDA;
   LayoutDev L = to_dev(layout);
   int64_t work = int64_t(num_tokens) * (L.head_size * L.elt_bytes / 16) * L.num_kv_heads * (v_pool ? 2 : 1);
+  const int per_tok = int(work / num_tokens);
+  if (per_tok <= 1024) {
+    const int threads = (per_tok + 31) / 32 * 32;
+    append_token_kernel<<<token_grid(append_token_kernel, num_tokens, threads), threads, 0,
+                          static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint8_t*>(k_pool), static_cast<uint8_t*>(v_pool),
+        static_cast<const uint8_t*>(k_src), static_cast<const uint8_t*>(v_src), slot_mapping, pos_dev,
+        pos_bias, num_tokens, L);
+    return cuda_status(cudaGetLastError());
+  }
   const int threads = 256;
-  append_kernel<<<grid_for(work, threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+  append_kernel<<<grid_for((work + kAppendUnroll - 1) / kAppendUnroll, threads), threads, 0,
+                  static_cast<cudaStream_t>(stream)>>>(
       static_cast<uint8_t*>(k_pool), static_cast<uint8_t*>(v_pool),
       static_cast<const uint8_t*>(k_src), static_cast<const uint8_t*>(v_src), slot_mapping, pos_dev,
       pos_bias, num_tokens, L);

@@ -26,6 +26,37 @@ def test_append_scatter_bit_exact(native_libs, oracle, dtype):
     assert np.array_equal(kvtest.from_device(vp, dtype).view(np.uint8), vr.view(np.uint8))
 
 
+@pytest.mark.parametrize("kv_heads,lens,k_only", [
+    (4, [6000, 5000, 1203], False),   # far more tokens than resident CTAs: every unrolled step of the token loop
+    (4, [6000, 5000, 1203], True),    # K pool alone (KVCacheLayer appends K and V in separate calls)
+    (40, [3000, 1500], False),        # a token wider than one CTA: the flat-index kernel, several passes
+])
+def test_append_large_and_wide_bit_exact(native_libs, oracle, kv_heads, lens, k_only):
+    import torch
+    from orinmllm_b200 import capi
+    dtype = "f16"
+    case = kvtest.make_paged_case(5, dtype, kv_heads, kv_heads, lens)
+    lay = capi.layout_paged(capi.dtype_code(kvtest.torch_dtype(dtype)), kv_heads, 128, 16, case.num_blocks)
+    shape = (case.num_blocks, kv_heads, 16, 128)
+    kp = kvtest.to_device(kvtest.poison(shape, dtype), dtype)
+    vp = kvtest.to_device(kvtest.poison(shape, dtype), dtype)
+    slots = case.slot_mapping.copy()
+    slots[::97] = -1  # padding tokens: skipped
+    case.slot_mapping = slots
+    d_slots = torch.from_numpy(slots).cuda()
+    if k_only:
+        capi.append(kp, None, lay, kvtest.to_device(case.k_rows, dtype), None, d_slots, num_tokens=case.total_tokens)
+    else:
+        capi.append(kp, vp, lay, kvtest.to_device(case.k_rows, dtype), kvtest.to_device(case.v_rows, dtype),
+                    d_slots, num_tokens=case.total_tokens)
+    kr, vr = kvtest.oracle_pools(oracle, case)
+    assert np.array_equal(kvtest.from_device(kp, dtype).view(np.uint8), kr.view(np.uint8))
+    if k_only:
+        assert np.array_equal(kvtest.from_device(vp, dtype).view(np.uint8), kvtest.poison(shape, dtype).view(np.uint8))
+    else:
+        assert np.array_equal(kvtest.from_device(vp, dtype).view(np.uint8), vr.view(np.uint8))
+
+
 def test_append_at_device_position_reference_layout(native_libs, oracle):
     """KVCacheLayer semantics: cache [S, kv_dim], row *pos (device int32) <- src."""
     import torch
