@@ -333,6 +333,24 @@ inline int grid_for(int64_t work_items, int threads) {
   return int(blocks);
 }
 
+// Grid of a grid-stride kernel capped at exactly what the SMs hold at once (from the occupancy
+// calculator, looked up once per kernel): a cap above that runs the surplus CTAs as a second,
+// partly filled wave.
+template <typename Kernel>
+inline int resident_grid_for(Kernel kernel, int64_t work_items, int threads) {
+  static int per_sm = 0;
+  if (per_sm == 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) n = 1;
+    per_sm = n;
+  }
+  const DeviceInfo& di = device_info();
+  int64_t blocks = (work_items + threads - 1) / threads;
+  const int64_t cap = int64_t(di.sm_count > 0 ? di.sm_count : 148) * per_sm;
+  if (blocks > cap) blocks = cap;
+  return int(blocks < 1 ? 1 : blocks);
+}
+
 // Grid of a token-walking kernel: one CTA per token up to what the SMs hold at once (from the
 // occupancy calculator, looked up once per kernel and CTA size).
 template <typename Kernel>
@@ -398,7 +416,7 @@ static int launch_rope(void* q, void* k, const void* v, int32_t q_heads, const i
                   ((v && v_pool) ? L.num_kv_heads * L.head_size / E : 0));
   if (work == 0) return KPX_OK;
   const int threads = 256;
-  rope_append_kernel<T><<<grid_for(work, threads), threads, 0, stream>>>(
+  rope_append_kernel<T><<<resident_grid_for(rope_append_kernel<T>, work, threads), threads, 0, stream>>>(
       static_cast<T*>(q), static_cast<T*>(k), static_cast<const T*>(v), q_heads, positions, pos_base,
       sin_cache, cos_cache, static_cast<uint8_t*>(k_pool), static_cast<uint8_t*>(v_pool),
       slot_mapping, num_tokens, L, q_norm_w, k_norm_w, norm_eps);

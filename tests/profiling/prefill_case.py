@@ -73,3 +73,29 @@ for c in range(NCH):
     print(f"chunk {c} queued: {ms * 1e3:8.1f} us  {flops[c] / ms / 1e9:8.1f} TFLOP/s (causal-exact)")
 print("status", capi.workspace_status(ws))
 print(f"all chunks (device time): {sum(flops) / total_ms / 1e9:.1f} TFLOP/s, {total_ms * 1e3:.1f} us per 4x2048-token prefill layer")
+
+# (3) the chunk step as the path runs it: RoPE + append of the chunk's 4 x 512 new rows into the
+#     pool, then the attention call; queued as in (2)
+k_new = torch.randn(B * CHUNK, HKV * D, device="cuda", dtype=dt)
+v_new = torch.randn(B * CHUNK, HKV * D, device="cuda", dtype=dt)
+sin = torch.empty(PROMPT * D, device="cuda", dtype=torch.float32)
+cos = torch.empty_like(sin)
+capi.sin_cos_cache(sin, cos, D, PROMPT, 1e6)
+step_ms = 0.0
+for c in range(NCH):
+    pos = np.tile(np.arange(c * CHUNK, (c + 1) * CHUNK), B).astype(np.int32)
+    seq = np.repeat(np.arange(B), CHUNK)
+    slots = table[seq, pos // BS].astype(np.int64) * BS + pos % BS
+    d_pos, d_slots = torch.from_numpy(pos).cuda(), torch.from_numpy(slots).cuda()
+    for _ in range(3):
+        filler.add_(1.0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(queued):
+        capi.rope_append(q, k_new, v_new, H, d_pos, sin, cos, kp, vp, lay, d_slots, B * CHUNK)
+        call(c)
+    e1.record()
+    torch.cuda.synchronize()
+    step_ms += e0.elapsed_time(e1) / queued
+print(f"all chunks with RoPE+append (device time): {step_ms * 1e3:.1f} us per layer = "
+      f"{B * PROMPT / step_ms / 1e3:.1f} M tokens/s per layer, {sum(flops) / step_ms / 1e9:.1f} TFLOP/s of attention")
