@@ -41,6 +41,10 @@ KPX_API int32_t kpx_sched_submit(kpx_sched* s, const int32_t* prompt, int32_t pr
 KPX_API int32_t kpx_sched_submit_turn(kpx_sched* s, const int32_t* prompt, int32_t prompt_len,
                                       int32_t max_new_tokens, int32_t also_register,
                                       const int32_t* turn_suffix, int32_t suffix_len);
+/* Sampled tokens that end a request before max_new_tokens (the reference's
+ * model.is_sentence_ending, demo/inference_common.h:1204); n = 0 clears the set.  The end
+ * token is kept as the request's last token (it has no K/V unless the turn's gap is filled). */
+KPX_API int kpx_sched_set_end_tokens(kpx_sched* s, const int32_t* token_ids, int32_t n);
 /* -> number of requests moved from waiting to running. */
 KPX_API int32_t kpx_sched_admit(kpx_sched* s);
 

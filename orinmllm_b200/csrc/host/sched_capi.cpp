@@ -1,5 +1,7 @@
 // C ABI of the request scheduler (include/kpx_sched.h) over base::KVScheduler.
 #include <cstring>
+#include <memory>
+#include <unordered_set>
 #include <vector>
 
 #include "base/kv_scheduler.h"
@@ -50,6 +52,16 @@ extern "C" int32_t kpx_sched_submit_turn(kpx_sched* s, const int32_t* prompt, in
   if (!s || !prompt || prompt_len <= 0 || suffix_len < 0 || (suffix_len > 0 && !turn_suffix)) return -1;
   return s->sched->submit_turn(std::vector<int32_t>(prompt, prompt + prompt_len), max_new_tokens,
                                std::vector<int32_t>(turn_suffix, turn_suffix + suffix_len), also_register);
+}
+extern "C" int kpx_sched_set_end_tokens(kpx_sched* s, const int32_t* token_ids, int32_t n) {
+  if (!s || n < 0 || (n > 0 && !token_ids)) return KPX_ERR_INVALID_ARGUMENT;
+  if (n == 0) {
+    s->sched->set_end_token_test(nullptr);
+    return KPX_OK;
+  }
+  auto ids = std::make_shared<std::unordered_set<int32_t>>(token_ids, token_ids + n);
+  s->sched->set_end_token_test([ids](int32_t t) { return ids->count(t) != 0; });
+  return KPX_OK;
 }
 extern "C" int32_t kpx_sched_admit(kpx_sched* s) { return s ? s->sched->admit() : -1; }
 

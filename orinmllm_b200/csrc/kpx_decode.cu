@@ -53,6 +53,7 @@ struct DecodeParams {
   int32_t head_groups;  // ceil(kv_mul / QH)
   int32_t partial_slots;  // slots of kPartialFloats floats in `partials`
   int32_t tile_contig;
+  int32_t min_blocks_per_range, min_warps_per_sm;  // read by the small-launch form of the kernel only
   float qscale;  // softmax scale * log2(e)
 };
 
@@ -140,7 +141,13 @@ __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-template <typename T, int QH, int NW, int NS, int LPT>
+// kSmall: the form launched when the host can tell from the batch size and the table width that
+// the launch has only a few blocks per warp (a short batch, or one KV head of one long
+// sequence).  It cuts the line into fewer, longer ranges: every piece of a cut item costs a
+// partial and a share of the assembly, and a range of a block or two is all prologue.  Warps
+// are then numbered CTA-minor so that the active ones stay spread over all SMs.  The policy
+// is compiled out of the other form, whose code is the same as without it.
+template <typename T, int QH, int NW, int NS, int LPT, bool kSmall = false>
 __global__ void __launch_bounds__(Cfg<T, QH, NW, NS, LPT>::kThreads, 1)
 paged_decode_kernel(const DecodeParams p) {
   using C = Cfg<T, QH, NW, NS, LPT>;
@@ -189,8 +196,21 @@ paged_decode_kernel(const DecodeParams p) {
     for (int e = tid; e < p.num_q_heads * kD; e += C::kThreads) o[e] = Elt<T>::from_float(0.f);
   }
   const int64_t total = int64_t(prefix[p.batch]) * p.num_kv_heads * p.head_groups;
-  const int64_t W = int64_t(gridDim.x) * C::kWarps;
-  const int64_t worker = int64_t(blockIdx.x) * C::kWarps + warp;
+  int64_t W_ = int64_t(gridDim.x) * C::kWarps;
+  int64_t worker_ = int64_t(blockIdx.x) * C::kWarps + warp;
+  if constexpr (kSmall) {
+    if (total < W_ * p.min_blocks_per_range) {
+      int64_t w = total / p.min_blocks_per_range;
+      const int64_t floor_w = int64_t(gridDim.x) * (C::kWarps < p.min_warps_per_sm ? C::kWarps : p.min_warps_per_sm);
+      if (w < floor_w) w = floor_w;
+      if (w < 1) w = 1;
+      if (w < W_) W_ = w;
+      worker_ = int64_t(warp) * gridDim.x + blockIdx.x;
+      if (worker_ >= W_) return;  // nothing below synchronises across warps
+    }
+  }
+  const int64_t W = W_;
+  const int64_t worker = worker_;
   Split split;
   split.quot = total / W;
   split.rem = total - split.quot * W;
@@ -498,7 +518,7 @@ paged_decode_kernel(const DecodeParams p) {
     // last of them to arrive into one slot of a second area, and the last group to finish
     // merges those.  The second area sits at the end of the slot array: [group slots][one
     // slot of group counters]; it is used only if the array has room for it.
-    constexpr int kGroup = 16, kFlatMax = 48;
+    constexpr int kGroup = 16, kFlatMax = 16;  // kFlatMax >= kGroup: a group then never holds more than two grouped items
     const int64_t W_all = int64_t(gridDim.x) * C::kWarps;
     const int64_t n_groups = (W_all + kGroup - 1) / kGroup;
     const int64_t group_base = int64_t(p.partial_slots) - 1 - 2 * n_groups;  // first group slot
@@ -752,14 +772,28 @@ constexpr int kStatusBytes = 256;
 
 // Tuning knob: 0 = default shape; set through kpx_internal_set_decode_variant.
 int g_decode_variant = 0;
+// Small launches (see paged_decode_kernel): used when batch x table width x items per sequence
+// is below g_small_below blocks per warp of the grid; then ranges hold at least
+// g_min_blocks_per_range blocks while at least g_min_warps_per_sm warps per SM stay active.
+int g_small_below = 12, g_min_blocks_per_range = 12, g_min_warps_per_sm = 4;
 
-template <typename T, int QH, int NW, int NS, int LPT>
+// True when the launch certainly has fewer than g_small_below blocks per warp.
+inline bool small_launch(const DecodeParams& p, int qh, int warps_per_cta) {
+  if (!p.block_table || g_small_below <= 0) return false;
+  int grid = device_info().sm_count;
+  if (grid > kMaxSms) grid = kMaxSms;
+  const int64_t groups = (p.kv_mul + qh - 1) / qh;
+  const int64_t bound = int64_t(p.batch) * p.max_blocks_per_seq * p.num_kv_heads * groups;
+  return bound < int64_t(grid) * warps_per_cta * g_small_below;
+}
+
+template <typename T, int QH, int NW, int NS, int LPT, bool kSmall = false>
 int launch_decode(DecodeParams p, cudaStream_t stream) {
   using C = Cfg<T, QH, NW, NS, LPT>;
   static int configured_dev = -1;
   int dev = 0;
   KPX_CUDA_TRY(cudaGetDevice(&dev));
-  auto kern = paged_decode_kernel<T, QH, NW, NS, LPT>;
+  auto kern = paged_decode_kernel<T, QH, NW, NS, LPT, kSmall>;
   if (configured_dev != dev) {
     KPX_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
     configured_dev = dev;
@@ -774,7 +808,9 @@ int launch_decode(DecodeParams p, cudaStream_t stream) {
 
 template <typename T, int QH>
 int launch_shape(const DecodeParams& p, cudaStream_t stream) {
-  if (sizeof(T) == 4) return launch_decode<T, QH, 6, 2, 8>(p, stream);
+  if (sizeof(T) == 4)
+    return small_launch(p, QH, 6) ? launch_decode<T, QH, 6, 2, 8, true>(p, stream)
+                                  : launch_decode<T, QH, 6, 2, 8>(p, stream);
   if (sizeof(T) == 2) {
     switch (g_decode_variant) {
       case 1: return launch_decode<T, QH, 8, 3, 8>(p, stream);
@@ -783,7 +819,8 @@ int launch_shape(const DecodeParams& p, cudaStream_t stream) {
       default: break;
     }
   }
-  return launch_decode<T, QH, 12, 2, 16>(p, stream);
+  return small_launch(p, QH, 12) ? launch_decode<T, QH, 12, 2, 16, true>(p, stream)
+                                 : launch_decode<T, QH, 12, 2, 16>(p, stream);
 }
 
 template <typename T>
@@ -802,6 +839,12 @@ using namespace kpx;
 
 extern "C" __attribute__((visibility("default"))) void kpx_internal_set_decode_variant(int v) {
   g_decode_variant = v;
+}
+extern "C" __attribute__((visibility("default"))) void kpx_internal_set_decode_small(int below, int min_blocks,
+                                                                                       int min_warps) {
+  g_small_below = below;
+  if (min_blocks > 0) g_min_blocks_per_range = min_blocks;
+  if (min_warps >= 0) g_min_warps_per_sm = min_warps;
 }
 
 extern "C" int64_t kpx_decode_workspace_bytes(int32_t batch, int32_t num_q_heads,
@@ -867,6 +910,8 @@ int kpx::decode_rows(void* out, const void* q, const void* k_pool, const void* v
   p.head_groups = 1;
   p.partial_slots = 2 * kMaxSms * kMaxWarpsPerCta;
   p.tile_contig = tile_contiguous(layout) ? 1 : 0;
+  p.min_blocks_per_range = g_min_blocks_per_range;
+  p.min_warps_per_sm = g_min_warps_per_sm;
   p.qscale = scale * kLog2e;
   // the block prefix of one launch lives in shared memory: long batches go in slices
   for (int32_t b0 = 0; b0 < batch; b0 += kMaxBatch) {

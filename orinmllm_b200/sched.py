@@ -17,6 +17,7 @@ SIGNATURES = {
     "kpx_sched_destroy": (None, [_P]),
     "kpx_sched_submit": (_I32, [_P, _P, _I32, _I32, _I32]),
     "kpx_sched_submit_turn": (_I32, [_P, _P, _I32, _I32, _I32, _P, _I32]),
+    "kpx_sched_set_end_tokens": (C.c_int, [_P, _P, _I32]),
     "kpx_sched_admit": (_I32, [_P]),
     "kpx_sched_next_prefill": (C.c_int, [_P]),
     "kpx_sched_prefill_shape": (C.c_int, [_P, _P, _P, _P]),
@@ -118,6 +119,13 @@ class Scheduler:
         if rid < 0:
             raise ValueError("kpx_sched_submit_turn refused the request")
         return rid
+
+    def set_end_tokens(self, token_ids):
+        """Sampled tokens that end a request early (kpx_sched_set_end_tokens); empty clears."""
+        ids = np.ascontiguousarray(token_ids, dtype=np.int32)
+        rc = lib().kpx_sched_set_end_tokens(self._h, _ptr(ids) if len(ids) else None, len(ids))
+        if rc != 0:
+            raise ValueError(f"kpx_sched_set_end_tokens: status {rc}")
 
     def admit(self) -> int:
         return lib().kpx_sched_admit(self._h)

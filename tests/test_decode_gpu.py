@@ -132,3 +132,25 @@ def test_decode_placement_invariance(native_libs, oracle):
                           torch.from_numpy(case.seq_lens).cuda(), 0, 3, 32, 1.0 / np.sqrt(128), ws, nbytes)
         outs.append(out.cpu())
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("knobs", [(0, 12, 4), (1 << 20, 20, 0), (1 << 20, 3, 1), (1 << 20, 12, 4)])
+@pytest.mark.parametrize("dtype,heads,lens", [
+    ("f16", (32, 8), [4096]),                 # one sequence: every item is cut into many pieces
+    ("bf16", (12, 2), [300, 9000, 17, 0, 64]),
+    ("f32", (8, 8), [2000, 1]),
+    ("f16", (4, 1), [40000]),                 # one KV head of one long sequence (the sharded case)
+])
+def test_decode_small_launch_forms(native_libs, oracle, knobs, dtype, heads, lens):
+    """Launches with few blocks per warp run a form of the kernel that cuts the work into fewer,
+    longer ranges on CTA-minor warp numbers.  Whatever the cut (off; as coarse as 20 blocks per
+    range with idle SMs allowed; as fine as 3), outputs meet the oracle, twice in a row on the
+    same workspace."""
+    from orinmllm_b200 import capi
+    lib = capi.lib()
+    try:
+        lib.kpx_internal_set_decode_small(*knobs)
+        case = kvtest.make_paged_case(29, dtype, heads[0], heads[1], lens)
+        _run_case(oracle, case, check_append=False, launches=2)
+    finally:
+        lib.kpx_internal_set_decode_small(12, 12, 4)

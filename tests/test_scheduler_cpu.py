@@ -216,3 +216,28 @@ def test_gap_fill_blocks_are_reserved_at_admission():
     st = s.stats()
     assert st["finished"] == 2 and st["admission_stalls"] > 0 and st["peak_blocks_in_use"] <= 8
     assert st["gap_tokens"] == 2 * 41 and m.num_free == 8
+
+
+def test_end_tokens_finish_a_request_early():
+    """kpx_sched_set_end_tokens: a sampled end token stops the request before max_new_tokens (the
+    reference's is_sentence_ending check, demo/inference_common.h:1204); with a turn suffix the
+    end token and the suffix are then prefilled and registered."""
+    m = kvm.KvManager(128, BS, seed=3)
+    s = sched.Scheduler(m)
+    s.set_end_tokens([151645, 151643])
+    prompt = np.arange(50, 90, dtype=np.int32)
+    # sampled: 11, 12, 151645 (end) ...
+    seq = iter([11, 12, 151645, 13, 14, 15, 16, 17])
+    a = s.submit_turn(prompt, 8, [198])
+    drive(s, sample=lambda rid, step: next(seq))
+    toks = s.tokens(a)
+    assert list(toks[len(prompt):]) == [11, 12, 151645, 198]
+    st = s.stats()
+    assert st["decoded_tokens"] == 2 and st["gap_tokens"] == 2 and st["finished"] == 1
+    b = s.submit(np.concatenate([toks, [7, 8, 9]]).astype(np.int32), 2)
+    drive(s, sample=lambda rid, step: 5)
+    assert s.reused_tokens(b) == len(toks)
+    s.set_end_tokens([])
+    c = s.submit(prompt + 1000, 3)
+    drive(s, sample=lambda rid, step: 151645)   # no longer an end token
+    assert len(s.tokens(c)) == len(prompt) + 3
