@@ -1,7 +1,8 @@
 """BASELINE.json configs[4](b): one 131072-token sequence at the Qwen3-8B attention shape sharded by
 KV head over the ranks (8 KV heads -> 8/G per GPU), NCCL all-gather of the per-head outputs.
 Reports, per layer-step, the decode kernel time (max over ranks), its KV GB/s per GPU, and the
-all-gather latency separately.  Run with 1 process or under torchrun:
+all-gather latency separately: behind the attention of the same step (includes the ranks'
+launch skew) and alone, back to back.  Run with 1 process or under torchrun:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node G --master-addr 127.0.0.1 \
         tests/profiling/long_seq_sharded.py
@@ -62,6 +63,18 @@ for _ in range(ITERS):
     torch.cuda.synchronize()
     t_attn.append(ev[0].elapsed_time(ev[1]))
     t_gather.append(ev[1].elapsed_time(ev[2]))
+# the all-gather alone: back to back, so that the ranks' launch skew after the barrier (which the
+# bracket above includes) drops out
+n_alone = 50
+torch.cuda.synchronize()
+if world > 1:
+    dist.barrier()
+ev[0].record()
+for _ in range(n_alone):
+    full = multigpu.gather_head_outputs(out, world)
+ev[1].record()
+torch.cuda.synchronize()
+alone = multigpu.max_over_ranks(ev[0].elapsed_time(ev[1]) / n_alone, world, dev)
 attn = multigpu.max_over_ranks(float(np.median(t_attn)), world, dev)
 gath = multigpu.max_over_ranks(float(np.median(t_gather)), world, dev)
 assert capi.workspace_status(ws) == 0 and full.shape[-1] == H * D
@@ -69,6 +82,7 @@ if rank == 0:
     kv_bytes = CTX * hkv * D * 2 * 2
     print(json.dumps({"n_gpus": world, "kv_heads_per_gpu": hkv, "ctx": CTX, "attention_us": round(attn * 1e3, 1),
                       "kv_gbs_per_gpu": round(kv_bytes / attn / 1e6, 1), "allgather_us": round(gath * 1e3, 1),
+                      "allgather_alone_us": round(alone * 1e3, 1),
                       "kv_mb_per_gpu": round(kv_bytes / 1e6, 1)}))
 if world > 1:
     dist.destroy_process_group()
