@@ -9,8 +9,9 @@
 // item completely writes its output directly; an item cut by a range boundary
 // leaves one partial (running max, sum, un-normalised accumulator) per warp in the
 // workspace, and the warp that delivers the item's last piece (an atomic counter per item,
-// nobody waits) assembles the output; an item cut into very many pieces (one very long
-// sequence) is assembled in two levels, 16 warps' pieces at a time.  One launch.
+// nobody waits) assembles the output; an item cut into more than 16 pieces is assembled in
+// two levels, 16 warps' pieces at a time.  One launch.  A launch that the host can tell to
+// be small (few blocks per warp) runs a second instantiation that cuts fewer, longer ranges.
 //
 // Each warp is its own producer and consumer: it owns two K and two V tile slots in
 // shared memory, fetches the (block, kv head) tiles of its range through the block
