@@ -98,8 +98,10 @@ class ClockSampler(threading.Thread):
 class DecodeWorkload:
     """Per-GPU state of the headline workload, resident in HBM."""
 
-    def __init__(self, rank, total_steps, device):
+    def __init__(self, rank, total_steps, device, chains=1, fused=True):
         import torch
+        self.chains, self.fused = chains, fused
+        self.per_layer = 1 if fused else 2
         from orinmllm_b200 import capi
         self.torch, self.capi, self.dev = torch, capi, device
         # weak scaling: every GPU gets the same amount of work (the same context lengths); block
@@ -140,8 +142,12 @@ class DecodeWorkload:
         self.cos = torch.empty(max_pos, HEAD, dtype=torch.float32, device=device)
         capi.sin_cos_cache(self.sin, self.cos, HEAD, max_pos, ROPE_THETA)
         self.ws_bytes = capi.decode_workspace_bytes(BATCH, Q_HEADS, KV_HEADS, HEAD)
-        self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=device)
-        capi.workspace_init(self.ws, self.ws_bytes)
+        # launches that may overlap on the GPU (layers captured on parallel chains) need a
+        # workspace each
+        self.wss = [torch.empty(self.ws_bytes, dtype=torch.uint8, device=device) for _ in range(max(1, chains))]
+        for w in self.wss:
+            capi.workspace_init(w, self.ws_bytes)
+        self.ws = self.wss[0]
         self.scale = 1.0 / float(np.sqrt(HEAD))
         self.launches = 0
         # host side of the end-to-end path
@@ -170,13 +176,25 @@ class DecodeWorkload:
         self.cur_slots = self.torch.empty(BATCH, dtype=self.torch.int64, device=self.dev)
         self.graph_resident = self.graph_e2e = None
 
-    def layer(self, t, l, events=None, stream=None):
+    def layer(self, t, l, events=None, stream=None, ws=None, flags=0):
         """RoPE + append + attend of layer l.  t: step index into the precomputed positions and
         slots, or None for the current-step buffers (graph capture)."""
         capi = self.capi
         stream = self.stream if stream is None else stream
         pos = self.cur_pos.data_ptr() if t is None else self.p_pos + t * BATCH * 4
         slots = self.cur_slots.data_ptr() if t is None else self.p_slots + t * BATCH * 8
+        if self.fused:
+            # one launch per layer: RoPE of the new rows, append, attention over cached + new
+            if events is not None:
+                events[0].record()
+            capi.rope_append_decode(self.p_out[l], self.p_q[l], self.p_k[l], self.p_v[l], self.p_sin, self.p_cos,
+                                    self.p_kpool[l], self.p_vpool[l], self.layout, self.p_table, self.max_blocks,
+                                    pos, BATCH, Q_HEADS, self.scale, self.p_ws if ws is None else ws,
+                                    self.ws_bytes, flags, stream=stream)
+            if events is not None:
+                events[1].record()
+            self.launches += 1
+            return
         capi.rope_append(self.p_q[l], self.p_k[l], self.p_v[l], Q_HEADS, pos, self.p_sin, self.p_cos,
                          self.p_kpool[l], self.p_vpool[l], self.layout, slots, BATCH, stream=stream)
         if events is not None:
@@ -184,7 +202,8 @@ class DecodeWorkload:
         # tokens cached before the step + 1 appended = attended length (len_bias = 1)
         capi.paged_decode(self.p_out[l], self.p_q[l], self.p_kpool[l], self.p_vpool[l], self.layout,
                           self.p_table, self.max_blocks, pos, 1, BATCH, Q_HEADS, self.scale,
-                          self.p_ws, self.ws_bytes, stream=stream)
+                          self.p_ws if ws is None else ws, self.ws_bytes, stream=stream)
+        # (the two-kernel path has no overlapped form: flags apply to the fused launch only)
         if events is not None:
             events[1].record()
         self.launches += 2
@@ -212,43 +231,60 @@ class DecodeWorkload:
         self.cur_slots.copy_(self.slots[t], non_blocking=True)
 
     def capture(self):
-        """Captures the resident step (72 kernels) and the end-to-end step (the same kernels with
-        every layer's host->device and device->host copies on side streams, so that copies of
-        one layer run under the kernels of its neighbours).  Capture executes nothing."""
+        """Captures the resident step and the end-to-end step (the same launches with every
+        layer's host->device and device->host copies on side streams, so that copies of one
+        layer run under the kernels of its neighbours).  Consecutive layers of this workload are
+        independent (own pool, own rows, own output), so layer l is captured on chain l % chains
+        with that chain's workspace: a layer's CTAs take over the SMs as the previous layer's
+        CTAs retire instead of waiting for its last warp.  Capture executes nothing."""
         torch = self.torch
         main, h2d, d2h = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
+        side = [torch.cuda.Stream(self.dev) for _ in range(self.chains)] if self.chains > 1 else [main]
+        flags = self.capi.KPX_DECODE_OVERLAPPED if self.chains > 1 else 0
         count = self.launches
+
+        def run_layer(l):
+            c = l % len(side)
+            self.layer(None, l, stream=side[c].cuda_stream, ws=self.wss[c].data_ptr(), flags=flags)
+            return side[c]
+
         self.graph_resident = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph_resident, stream=main):
+            for s_ in side:
+                if s_ is not main:
+                    s_.wait_stream(main)
             for l in range(LAYERS):
-                self.layer(None, l, stream=main.cuda_stream)
+                run_layer(l)
+            for s_ in side:
+                if s_ is not main:
+                    main.wait_stream(s_)
         self.graph_e2e = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph_e2e, stream=main):
-            h2d.wait_stream(main)
-            d2h.wait_stream(main)
+            for s_ in [h2d, d2h] + [x for x in side if x is not main]:
+                s_.wait_stream(main)
             for l in range(LAYERS):
                 with torch.cuda.stream(h2d):
                     self.q[l].copy_(self.h_q[l], non_blocking=True)
                     self.k[l].copy_(self.h_k[l], non_blocking=True)
                     self.v[l].copy_(self.h_v[l], non_blocking=True)
-                main.wait_stream(h2d)
-                self.layer(None, l, stream=main.cuda_stream)
-                d2h.wait_stream(main)
+                side[l % len(side)].wait_stream(h2d)
+                ran_on = run_layer(l)
+                d2h.wait_stream(ran_on)
                 with torch.cuda.stream(d2h):
                     self.h_out[l].copy_(self.out[l], non_blocking=True)
-            main.wait_stream(h2d)
-            main.wait_stream(d2h)
+            for s_ in [h2d, d2h] + [x for x in side if x is not main]:
+                main.wait_stream(s_)
         self.launches = count  # capture launched nothing
 
     def replay_resident(self, t):
         self._set_step(t)
         self.graph_resident.replay()
-        self.launches += 2 * LAYERS
+        self.launches += self.per_layer * LAYERS
 
     def replay_e2e(self, t):
         self._set_step(t)
         self.graph_e2e.replay()
-        self.launches += 2 * LAYERS
+        self.launches += self.per_layer * LAYERS
 
     def kv_bytes_step(self, t):
         return kv_bytes_per_layer(self.lens0 + t + 1) * LAYERS
@@ -337,7 +373,10 @@ def run_gpu(args):
     W, K = args.warmup, args.steps
     use_graph = not args.no_graph
     total_steps = 2 * (W + K) + K + 2
-    wl = DecodeWorkload(rank, total_steps, device)
+    wl = DecodeWorkload(rank, total_steps, device, chains=max(1, args.chains) if use_graph else 1,
+                        fused=not args.unfused)
+    if args.variant:
+        wl.capi.lib().kpx_internal_set_decode_variant(args.variant)
 
     def barrier():
         if world > 1:
@@ -406,9 +445,10 @@ def run_gpu(args):
     barrier()
     ms_e2e = max_over_ranks(e0.elapsed_time(e1))
     clocks = sampler.stop() if sampler else None
-    status = wl.capi.workspace_status(wl.ws)
-    if status != 0:
-        raise SystemExit(f"device status {status}: {wl.capi.status_string(status)}")
+    for w in wl.wss:
+        status = wl.capi.workspace_status(w)
+        if status != 0:
+            raise SystemExit(f"device status {status}: {wl.capi.status_string(status)}")
     # whole-job totals (every rank holds the same amount of work: weak scaling)
     tot = multigpu.sum_over_ranks([bytes_resident, bytes_e2e], world, device)
     if rank != 0:
@@ -468,6 +508,11 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--chains", type=int, default=3,
+                    help="parallel chains the graph's independent layers are captured on")
+    ap.add_argument("--unfused", action="store_true",
+                    help="two launches per layer (kpx_rope_append, kpx_paged_decode) instead of one")
+    ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel separately instead of replaying CUDA graphs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup

@@ -149,6 +149,32 @@ KPX_API int kpx_paged_decode(void* out, const void* q, const void* k_pool, const
                              int32_t len_bias, int32_t batch, int32_t num_q_heads, float scale,
                              void* workspace, int64_t workspace_bytes, void* stream);
 
+/* One whole decode step of a layer in one launch: RoPE of the new token's Q and K rows,
+ * append of its K / V rows to the pool, and the attention of kpx_paged_decode over the cached
+ * tokens plus the new one.  positions[b] (device int32) is both the number of tokens sequence
+ * b already has in the pool and the position of its new token; q [batch, num_q_heads*head_size],
+ * k_new / v_new [batch, kv_heads*head_size] are read (not rotated in place); sin/cos tables as in
+ * kpx_rope_append.  The new token goes to row positions[b] % block_size of block
+ * block_table[b][positions[b] / block_size] (identity table if NULL), stored with the same bits
+ * kpx_rope_append stores; the attention takes it from registers, so the launch never reads what
+ * it writes.  Each (sequence, kv head) row pair is stored by the warp that finishes that
+ * sequence's last cached block.  Workspace, status word and capture rules as kpx_paged_decode.
+ * flags: KPX_DECODE_OVERLAPPED when the caller runs this launch concurrently with other launches
+ * of this library (another stream, ANOTHER workspace): the kernel then uses three small CTAs per
+ * SM so that SMs pass from one launch to the next in thirds; 0 otherwise.
+ * Replaces the decode-step sequence RoPEGpuPosLayer -> KVCacheLayer(K), KVCacheLayer(V) ->
+ * FlashAttentionDecodeLayer / MHAGpuPosLayer of attention_qkv_with_graph and
+ * attention_mha_with_graph (kuiper/source/model/qwen3.cpp:1052-1127,
+ * kuiper/source/model/qwen_base.cpp:145-192). */
+enum { KPX_DECODE_OVERLAPPED = 1 };
+KPX_API int kpx_rope_append_decode(void* out, const void* q, const void* k_new, const void* v_new,
+                                   const float* sin_cache, const float* cos_cache, void* k_pool,
+                                   void* v_pool, const kpx_kv_layout* layout,
+                                   const int32_t* block_table, int32_t max_blocks_per_seq,
+                                   const int32_t* positions, int32_t batch, int32_t num_q_heads,
+                                   float scale, void* workspace, int64_t workspace_bytes,
+                                   int32_t flags, void* stream);
+
 /* kpx_paged_decode for callers that cannot allocate or pass scratch memory: a plugin
  * inside a host that owns the device heap, a kernel registry whose signature carries only
  * inputs and outputs (the reference's MHAKernel is one), code that may not call cudaMalloc

@@ -5,18 +5,23 @@
  * against and the timed CPU baseline; nothing in the product library links,
  * loads or calls it.
  *
- * Parity status: the reference ships no golden vectors for attention, RoPE or
- * the KV append (its tests for these pieces are commented out and draw from an
- * unseeded random_device), and its CPU kernels need Armadillo + glog which are
- * not installed, so the arithmetic below is pinned by restatement only:
- * "parity unpinned" for the floating-point functions in this file.  The integer
- * paths (radix tree / prefix cache) are pinned separately against the reference
- * headers compiled directly (see oracle/Makefile, target _ref).
+ * Parity status: pinned against the reference itself.  The reference ships no golden
+ * vectors for attention, RoPE or the KV append (its tests for these pieces are commented
+ * out and draw from an unseeded random_device), so the pin is the reference's own CPU
+ * kernels run on seeded inputs: cpu/{mha,matmul,softmax,scale_sum,rope,rmsnorm}_kernel.cpp
+ * with tensor.cpp and the allocator sources compile unmodified against small stand-ins
+ * for their two third-party headers (oracle/shim/, oracle/ref_cpu_glue.cpp; Makefile target
+ * `ref`), and tests/test_oracle_ref_cpu.py requires this file to reproduce their outputs
+ * bit for bit when the stand-in's reductions run in index order, and within 1e-6 when
+ * they run as Armadillo's own two-running-sums loops do.  The outputs are also committed
+ * as tests/golden/ref_cpu_golden.npz for machines without the reference checkout.  The
+ * integer paths (radix tree / prefix cache) are pinned separately against the reference
+ * headers compiled directly.
  *
- * The Armadillo expressions at the reference call sites reduce to: a 128-long
- * dot product (fmat 1xK times Kx1), element-wise exp, a sum, a scalar*vector
- * and a vector +=.  Armadillo does not define the summation order of the dot
- * product, so orc_mha accumulates sequentially in fp32 and orc_mha_f64 gives a
+ * The Armadillo expressions at the reference call sites reduce to: a 128-long dot
+ * product (fmat 1xK times Kx1), element-wise exp, a sum, a scalar*vector and a vector +=.
+ * Armadillo does not define the summation order of the dot product (with a BLAS it is
+ * the BLAS's), so orc_mha accumulates sequentially in fp32 and orc_mha_f64 gives a
  * float64 shadow to bound the oracle's own rounding error.
  *
  * Every function names the reference lines it follows (paths are relative to

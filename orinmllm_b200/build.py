@@ -7,7 +7,8 @@ Produces, next to this file under ``lib/``:
   libkpx.so          CUDA kernels + the C ABI declared in include/kpx.h
   libkuiper_b200.so  C++ host layer (kuiper-style op::Layer adapters, kernel registry,
                      block pool manager, radix tree / prefix cache) on top of libkpx
-The CPU checker under ``oracle/`` is built by its own Makefile (see build_oracle()).
+The CPU checker under ``oracle/`` and the C++ test program are test infrastructure and are
+built by tests/buildtools.py, not from here.
 """
 from __future__ import annotations
 
@@ -113,33 +114,6 @@ def build_host(force=False, verbose=False) -> Path | None:
     return so
 
 
-def build_oracle(verbose=False) -> Path:
-    """Build the CPU checker (test infrastructure) and, where the reference checkout is
-    present, the reference-compiled radix programs under oracle/_ref/."""
-    odir = ROOT / "oracle"
-    _run(["make", "-C", odir, "all"], verbose)
-    if Path(os.environ.get("KPX_REFERENCE", "/root/reference")).joinpath(
-            "kuiper/include/base/radix_tree.h").exists():
-        _run(["make", "-C", odir, "ref",
-              f"REF={os.environ.get('KPX_REFERENCE', '/root/reference')}"], verbose)
-    return odir / "liborinkv_oracle.so"
-
-
-def build_cpp_tests(force=False, verbose=False) -> Path:
-    """Compile tests/cpp/test_kuiper_api.cu (layer API vs the CPU oracle; test infrastructure,
-    the only binary that links the oracle) into lib/test_kuiper_api."""
-    src = ROOT / "tests" / "cpp" / "test_kuiper_api.cu"
-    exe = LIB / "test_kuiper_api"
-    oracle_so = build_oracle(verbose)
-    if force or _newer(exe, [src, LIB / "libkpx.so", oracle_so] + _headers()):
-        _run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17",
-              "-I", INCLUDE, "-I", INCLUDE / "kuiper", "-o", exe, src, f"-L{LIB}", "-lkpx",
-              f"-L{ROOT / 'oracle'}", "-lorinkv_oracle",
-              "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN",
-              "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../oracle"], verbose)
-    return exe
-
-
 def build_all(force=False, verbose=False, ptxas_info=False):
     build_kpx(force, verbose, ptxas_info)
     build_host(force, verbose)
@@ -150,9 +124,6 @@ if __name__ == "__main__":
     ap.add_argument("--force", action="store_true")
     ap.add_argument("-v", "--verbose", action="store_true")
     ap.add_argument("--ptxas", action="store_true", help="print registers / spills / smem per kernel")
-    ap.add_argument("--oracle", action="store_true", help="also build the CPU checker")
     a = ap.parse_args()
     build_all(a.force, a.verbose, a.ptxas)
-    if a.oracle:
-        build_oracle(a.verbose)
     print("built:", ", ".join(p.name for p in sorted(LIB.glob("*.so"))))

@@ -57,6 +57,8 @@ SIGNATURES = {
     "kpx_decode_workspace_bytes": (_I64, [_I32, _I32, _I32, _I32]),
     "kpx_paged_decode": (C.c_int, [_P, _P, _P, _P, _LP, _P, _I32, _P, _I32, _I32, _I32, _F32,
                                    _P, _I64, _P]),
+    "kpx_rope_append_decode": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _LP, _P, _I32, _P, _I32, _I32, _F32,
+                                         _P, _I64, _I32, _P]),
     "kpx_paged_decode_static": (C.c_int, [_P, _P, _P, _P, _LP, _P, _I32, _P, _I32, _I32, _I32, _F32, _P]),
     "kpx_workspace_init": (C.c_int, [_P, _I64, _P]),
     "kpx_workspace_status": (C.c_int, [_P, _P]),
@@ -193,6 +195,20 @@ def paged_decode(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq
                                  ptr(block_table), max_blocks_per_seq, ptr(seq_lens), len_bias,
                                  batch, num_q_heads, scale, ptr(workspace), workspace_bytes,
                                  _stream(stream)), "kpx_paged_decode")
+
+
+KPX_DECODE_OVERLAPPED = 1
+
+
+def rope_append_decode(out, q, k_new, v_new, sin_cache, cos_cache, k_pool, v_pool, layout, block_table,
+                       max_blocks_per_seq, positions, batch, num_q_heads, scale, workspace,
+                       workspace_bytes, flags=0, stream=None) -> None:
+    """One decode step of a layer in one launch (RoPE + append + attention)."""
+    check(lib().kpx_rope_append_decode(ptr(out), ptr(q), ptr(k_new), ptr(v_new), ptr(sin_cache),
+                                       ptr(cos_cache), ptr(k_pool), ptr(v_pool), C.byref(layout),
+                                       ptr(block_table), max_blocks_per_seq, ptr(positions), batch,
+                                       num_q_heads, scale, ptr(workspace), workspace_bytes, flags,
+                                       _stream(stream)), "kpx_rope_append_decode")
 
 
 def paged_decode_static(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq, seq_lens,

@@ -47,11 +47,20 @@ const DeviceInfo& device_info();  // for the current device, cached per device
 // kpx_paged_decode with one more degree of freedom: batch entry b reads block-table row
 // row_index[b] (device int32; nullptr = row b).  Chunked prefill uses it to run every query
 // token as its own single-query attention over its sequence's row.
+// With `fused` the launch is a whole decode step: seq_lens are the cached lengths (= the new
+// tokens' positions), the new token's q / k rows are rotated, its k / v rows stored into the
+// pools (which are written) and attended to.  `flags`: KPX_DECODE_* bits.
+struct FusedStep {
+  const void* k_new;
+  const void* v_new;
+  const float* sin_cache;
+  const float* cos_cache;
+};
 int decode_rows(void* out, const void* q, const void* k_pool, const void* v_pool,
                 const kpx_kv_layout* layout, const int32_t* block_table, int32_t max_blocks_per_seq,
                 const int32_t* row_index, const int32_t* seq_lens, int32_t len_bias, int32_t batch,
                 int32_t num_q_heads, float scale, void* workspace, int64_t workspace_bytes,
-                void* stream);
+                void* stream, const FusedStep* fused = nullptr, int flags = 0);
 
 // ---- device-side helpers -------------------------------------------------------------
 #ifdef __CUDACC__

@@ -9,8 +9,8 @@ pytestmark = pytest.mark.gpu
 
 
 def test_layer_api_program(native_libs):
-    from orinmllm_b200 import build
-    exe = build.build_cpp_tests()
+    from tests import buildtools
+    exe = buildtools.build_cpp_tests()
     res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
     print(res.stdout[-3000:])
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]

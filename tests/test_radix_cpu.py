@@ -14,7 +14,9 @@ import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
 GOLDEN = ROOT / "tests" / "golden"
-REF = Path(os.environ.get("KPX_REFERENCE", "/root/reference"))
+from tests import buildtools  # noqa: E402
+
+REF = buildtools.reference_checkout() or Path("/nonexistent")
 NAMES = ["tree_a", "tree_b", "cache_a", "cache_b", "config4"]
 
 
