@@ -90,12 +90,15 @@ class KVScheduler {
   const KVSchedulerConfig& config() const { return config_; }
   const KVSchedulerStats& stats() const { return stats_; }
 
-  // Queues a request; returns its id (ids count up from 0) or -1 on bad arguments.
+  // Queues a request; returns its id (ids count up from 0) or -1 on bad arguments, among them a
+  // request whose last token could never be cached because the whole pool is too small for it
+  // (it would otherwise wait at the head of the queue for ever).
   // also_register > 0: when the request finishes, its first also_register tokens are
   // registered as a prefix of their own as well (a shared system prompt: the tree only
   // reports a hit at a registered length, radix_tree.h:375-449).
   int32_t submit(const std::vector<int32_t>& prompt, int32_t max_new_tokens, int32_t also_register = 0) {
     if (prompt.empty() || max_new_tokens < 1 || also_register < 0) return -1;
+    if (blocks_for(static_cast<int32_t>(prompt.size()) + max_new_tokens - 1) > pool_->config().num_blocks) return -1;
     const int32_t id = next_id_++;
     Request& r = requests_[id];
     r.tokens = prompt;
@@ -113,6 +116,10 @@ class KVScheduler {
   // that the registered sequence is the whole history the next turn starts with.
   int32_t submit_turn(const std::vector<int32_t>& prompt, int32_t max_new_tokens,
                       const std::vector<int32_t>& turn_suffix, int32_t also_register = 0) {
+    if (prompt.empty() || max_new_tokens < 1) return -1;
+    // with the gap fill the history grows by the last sampled token and the suffix
+    const int64_t final_tokens = static_cast<int64_t>(prompt.size()) + max_new_tokens + static_cast<int64_t>(turn_suffix.size());
+    if (final_tokens > static_cast<int64_t>(pool_->config().num_blocks) * pool_->config().block_size) return -1;
     const int32_t id = submit(prompt, max_new_tokens, also_register);
     if (id < 0) return id;
     Request& r = requests_[id];
@@ -321,8 +328,10 @@ class KVScheduler {
     const int32_t need = blocks_for(final_len(r)) - mapped + ((reused % bs) != 0 ? 1 : 0);
     int32_t avail = pool_->num_free() - reserved_total_;
     if (need > avail && config_.use_prefix_cache && cache_) {
-      // spans nobody references can make room (oldest first)
-      cache_->evict(static_cast<int64_t>(need - avail) * bs);
+      // Spans nobody references make room, oldest first, and only as many as it takes.  (The
+      // cache's evict() would be the wrong tool: its argument is the token count to keep, and
+      // its token accounting does not map one to one onto blocks.)
+      cache_->reclaim_blocks([&] { return pool_->num_free() - reserved_total_ >= need; });
       avail = pool_->num_free() - reserved_total_;
     }
     if (need > avail) {

@@ -166,6 +166,17 @@ class PrefixCache {
     return gone;
   }
 
+  // Frees pool blocks for an allocator that is short: unreferenced spans go, oldest first,
+  // until `enough()` is true (RadixTree::reclaim_blocks).  Counted like an eviction.
+  int64_t reclaim_blocks(const std::function<bool()>& enough) {
+    const int64_t gone = tree_->reclaim_blocks(enough);
+    if (gone > 0 && config_.enable_stats) {
+      stats_.eviction_count += 1;
+      stats_.tokens_evicted += gone;
+    }
+    return gone;
+  }
+
   const PrefixCacheStats& get_stats() const { return stats_; }
   void reset_stats() { stats_.reset(); }
   const PrefixCacheConfig& get_config() const { return config_; }

@@ -188,6 +188,34 @@ class RadixTree {
     return freed;
   }
 
+  // Block-aware reclamation for an allocator under pressure (no counterpart in the reference,
+  // whose eviction above only trims a token count): drops unreferenced terminals that hold pool
+  // blocks, least recently used first, one at a time, until `enough()` answers true or none is
+  // left.  Unlike evict_lru it also takes terminals that have children: every terminal holds
+  // its own references on the blocks of its span, so dropping a parent never takes blocks away
+  // from a longer registered sequence below it, and spans that only ever gain children (a
+  // shared system prompt, earlier turns of a conversation) stay reclaimable.  Returns the
+  // kv_length total of what was dropped.
+  int64_t reclaim_blocks(const std::function<bool()>& enough) {
+    std::lock_guard<std::mutex> guard(mutex_);
+    if (enough()) return 0;
+    std::vector<std::shared_ptr<RadixNode>> holders;
+    gather_block_holders(root_, &holders);
+    std::stable_sort(holders.begin(), holders.end(),
+                     [](const std::shared_ptr<RadixNode>& a, const std::shared_ptr<RadixNode>& b) {
+                       return a->kv_info.last_access_time < b->kv_info.last_access_time;
+                     });
+    int64_t freed = 0;
+    for (const auto& node : holders) {
+      if (enough()) break;
+      const int64_t span = node->kv_info.kv_length;
+      drop_terminal(node);
+      total_cached_tokens_ -= span;
+      freed += span;
+    }
+    return freed;
+  }
+
   std::string dump() const {
     std::lock_guard<std::mutex> guard(mutex_);
     std::stringstream out;
@@ -352,6 +380,13 @@ class RadixTree {
                               std::vector<std::shared_ptr<RadixNode>>* out) const {
     if (node->is_terminal && node->is_leaf()) out->push_back(node);
     for (const auto& kv : node->children) gather_terminal_leaves(kv.second, out);
+  }
+
+  void gather_block_holders(const std::shared_ptr<RadixNode>& node,
+                            std::vector<std::shared_ptr<RadixNode>>* out) const {
+    if (node->is_terminal && node->kv_info.ref_count == 0 && !node->kv_info.block_ids.empty())
+      out->push_back(node);
+    for (const auto& kv : node->children) gather_block_holders(kv.second, out);
   }
 
   void release_subtree(const std::shared_ptr<RadixNode>& node) {

@@ -116,6 +116,7 @@ int kpx::decode_rows(void* out, const void* q, const void* k_pool, const void* v
   p.tile_contig = tile_contiguous(layout) ? 1 : 0;
   p.min_blocks_per_range = g_min_blocks_per_range;
   p.min_warps_per_sm = g_min_warps_per_sm;
+  p.debug = g_decode_variant & ~3;
   p.qscale = scale * kLog2e;
   // the block prefix of one launch lives in shared memory: long batches go in slices
   for (int32_t b0 = 0; b0 < batch; b0 += kMaxBatch) {

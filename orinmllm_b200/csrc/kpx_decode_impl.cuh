@@ -71,6 +71,7 @@ struct DecodeParams {
   int32_t partial_slots;  // slots of kPartialFloats floats in `partials`
   int32_t tile_contig;
   int32_t min_blocks_per_range, min_warps_per_sm;  // read by the small-launch form of the kernel only
+  int32_t debug;  // EXPERIMENT: timing-only switches
   float qscale;  // softmax scale * log2(e)
 };
 
@@ -365,7 +366,7 @@ paged_decode_kernel(const DecodeParams p) {
 #pragma unroll
       for (int c = 0; c < NCH; ++c) {
         float f[E];
-        if (kFused) {
+        if (kFused && !(p.debug & 8)) {
           // fused step: rotate the query at the new token's position (= cached length)
           const int d0 = coff[c] / C::kEltB, j0 = d0 & (kD / 2 - 1);
           float sn[E], cs[E];
@@ -468,7 +469,7 @@ paged_decode_kernel(const DecodeParams p) {
       mh[0] = m_run[0];
       lh[0] = l_run[0];
     }
-    if (kFused && has_item_end) {
+    if (kFused && has_item_end && !(p.debug & 4)) {
       // Fused step: this piece ends the item, so it also carries the new token (position
       // item.len, not in the pool yet).  Its rotated K row and its V row come from the
       // caller's rows; every token group computes the same update for its dims.
@@ -964,7 +965,7 @@ int launch_shape(const DecodeParams& p, cudaStream_t stream, int flags) {
                       : launch_decode<T, QH, 6, 2, 8>(p, stream);
   }
   // tuning knob for experiments: 1 forces the three-small-CTAs form, 2 the one-large-CTA form
-  const bool small_ctas = g_decode_variant == 1 ? true : (g_decode_variant == 2 ? false : overlapped);
+  const bool small_ctas = (g_decode_variant & 3) == 1 ? true : ((g_decode_variant & 3) == 2 ? false : overlapped);
   if (small_launch(p, QH, 12)) return launch_decode<T, QH, 12, 2, 16, true>(p, stream);
   return small_ctas ? launch_decode<T, QH, 4, 2, 16, false, 3>(p, stream)
                     : launch_decode<T, QH, 12, 2, 16>(p, stream);

@@ -241,3 +241,81 @@ def test_end_tokens_finish_a_request_early():
     c = s.submit(prompt + 1000, 3)
     drive(s, sample=lambda rid, step: 151645)   # no longer an end token
     assert len(s.tokens(c)) == len(prompt) + 3
+
+
+def test_admission_reclaims_cached_blocks_when_the_pool_is_short():
+    """An idle pool whose free blocks plus the blocks held by unreferenced cached spans cover a
+    request must admit it: 8 blocks, a finished 40-token request keeps 3 in the tree, the next
+    request needs all 8."""
+    m = kvm.KvManager(8, BS, seed=1)
+    s = sched.Scheduler(m)
+    a = s.submit(np.arange(40, dtype=np.int32), 1)
+    drive(s)
+    assert s.state(a) == 3 and m.num_free == 5 and m.cached_tokens == 40
+    b = s.submit(np.arange(1000, 1100, dtype=np.int32), 8 * BS - 100 + 1)  # last cached token is number 128
+    assert s.admit() == 1, "the request fits once the cached span is dropped"
+    drive(s)
+    assert s.state(b) == 3
+    assert m.prefix_stats()["eviction_count"] >= 1
+
+
+def test_small_shortfall_drops_only_the_oldest_span():
+    import time
+    m = kvm.KvManager(16, BS, seed=2)
+    s = sched.Scheduler(m)
+    prompts = [np.arange(100 * i, 100 * i + 48, dtype=np.int32) for i in range(1, 5)]  # 3 blocks each
+    for p in prompts:
+        s.submit(p, 1)
+        drive(s)
+        time.sleep(0.003)  # distinct last-access times (milliseconds)
+    assert m.num_free == 4
+    # needs 6 blocks: 2 short, so exactly one 3-block span (the oldest) has to go
+    c = s.submit(np.arange(5000, 5090, dtype=np.int32), 7)
+    assert s.admit() == 1
+    assert m.cached_tokens == 3 * 48
+    # the three younger prompts still hit, the oldest does not (looked up through the pool
+    # manager, which maps blocks by reference and allocates nothing)
+    hits = []
+    for p in prompts:
+        seq = m.add_sequence()
+        n = m.match_prefix(seq, np.concatenate([p, [7, 8, 9]]).astype(np.int32))
+        if n:
+            m.release_prefix(p[:n])
+        m.free_sequence(seq)
+        hits.append(n)
+    assert hits == [0, 48, 48, 48]
+    drive(s)
+    assert s.state(c) == 3
+
+
+def test_request_larger_than_the_pool_is_refused_at_submit():
+    m = kvm.KvManager(8, BS, seed=3)
+    s = sched.Scheduler(m)
+    with pytest.raises(ValueError):
+        s.submit(np.arange(100, dtype=np.int32), 8 * BS - 100 + 2)   # last cached token would be number 129
+    with pytest.raises(ValueError):
+        s.submit_turn(np.arange(100, dtype=np.int32), 20, turn_suffix=[1] * 9)   # 100 + 20 + 9 > 128
+    ok = s.submit(np.arange(100, dtype=np.int32), 8 * BS - 100 + 1)
+    drive(s)
+    assert s.state(ok) == 3
+
+
+def test_multi_turn_histories_are_reclaimable_without_clear():
+    """Every turn registers a longer history on top of the previous one, so the earlier spans
+    become inner nodes of the tree.  They must still give their blocks back under pressure."""
+    nblocks = 24
+    m = kvm.KvManager(nblocks, BS, seed=5)
+    s = sched.Scheduler(m, prefill_chunk=16)
+    hist = np.arange(300, 330, dtype=np.int32)
+    for turn in range(4):
+        rid = s.submit_turn(hist, 6, turn_suffix=[198, 199], also_register=len(hist) if turn == 0 else 0)
+        drive(s, sample=lambda r, step: 900 + step)
+        hist = np.concatenate([s.tokens(rid), np.arange(4000 + 10 * turn, 4010 + 10 * turn, dtype=np.int32)])
+    held = nblocks - m.num_free
+    assert held > 0 and m.prefix_stats()["cache_hits"] == 3
+    # a request that needs the whole pool: only possible if every span can be dropped
+    big = s.submit(np.arange(9000, 9000 + 200, dtype=np.int32), nblocks * BS - 200 + 1)
+    assert s.admit() == 1
+    assert m.cached_tokens == 0
+    drive(s)
+    assert s.state(big) == 3
