@@ -200,10 +200,10 @@ class DecodeWorkload:
         if events is not None:
             events[0].record()
         # tokens cached before the step + 1 appended = attended length (len_bias = 1)
-        capi.paged_decode(self.p_out[l], self.p_q[l], self.p_kpool[l], self.p_vpool[l], self.layout,
-                          self.p_table, self.max_blocks, pos, 1, BATCH, Q_HEADS, self.scale,
-                          self.p_ws if ws is None else ws, self.ws_bytes, stream=stream)
-        # (the two-kernel path has no overlapped form: flags apply to the fused launch only)
+        decode = capi.paged_decode_overlapped if flags & capi.KPX_DECODE_OVERLAPPED else capi.paged_decode
+        decode(self.p_out[l], self.p_q[l], self.p_kpool[l], self.p_vpool[l], self.layout,
+               self.p_table, self.max_blocks, pos, 1, BATCH, Q_HEADS, self.scale,
+               self.p_ws if ws is None else ws, self.ws_bytes, stream=stream)
         if events is not None:
             events[1].record()
         self.launches += 2
@@ -374,7 +374,7 @@ def run_gpu(args):
     use_graph = not args.no_graph
     total_steps = 2 * (W + K) + K + 2
     wl = DecodeWorkload(rank, total_steps, device, chains=max(1, args.chains) if use_graph else 1,
-                        fused=not args.unfused)
+                        fused=args.fused)
     if args.variant:
         wl.capi.lib().kpx_internal_set_decode_variant(args.variant)
 
@@ -510,8 +510,8 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--chains", type=int, default=3,
                     help="parallel chains the graph's independent layers are captured on")
-    ap.add_argument("--unfused", action="store_true",
-                    help="two launches per layer (kpx_rope_append, kpx_paged_decode) instead of one")
+    ap.add_argument("--fused", action="store_true",
+                    help="one launch per layer (kpx_rope_append_decode) instead of kpx_rope_append + kpx_paged_decode")
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel separately instead of replaying CUDA graphs")
     args = ap.parse_args()

@@ -149,6 +149,19 @@ KPX_API int kpx_paged_decode(void* out, const void* q, const void* k_pool, const
                              int32_t len_bias, int32_t batch, int32_t num_q_heads, float scale,
                              void* workspace, int64_t workspace_bytes, void* stream);
 
+/* kpx_paged_decode for launches that the caller overlaps on the GPU with other launches of
+ * this library (consecutive layers or requests on different streams, each launch with ITS OWN
+ * workspace).  Same arguments and results.  The kernel then runs as three CTAs of four warps per
+ * SM instead of one CTA of twelve, so that an SM passes from one launch to the next a third at
+ * a time while the earlier launch's last warps finish; run alone, kpx_paged_decode's single
+ * large CTA is the faster form.  No reference counterpart (the reference runs one kernel at a
+ * time on one stream). */
+KPX_API int kpx_paged_decode_overlapped(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                        const kpx_kv_layout* layout, const int32_t* block_table,
+                                        int32_t max_blocks_per_seq, const int32_t* seq_lens,
+                                        int32_t len_bias, int32_t batch, int32_t num_q_heads, float scale,
+                                        void* workspace, int64_t workspace_bytes, void* stream);
+
 /* One whole decode step of a layer in one launch: RoPE of the new token's Q and K rows,
  * append of its K / V rows to the pool, and the attention of kpx_paged_decode over the cached
  * tokens plus the new one.  positions[b] (device int32) is both the number of tokens sequence
@@ -201,8 +214,14 @@ KPX_API int kpx_paged_decode_static(void* out, const void* q, const void* k_pool
  * `stream`); call it once after allocating a workspace.  kpx_workspace_status
  * synchronises the stream, returns the word -- KPX_OK, KPX_ERR_DEVICE_TIMEOUT if a
  * bounded device-side wait gave up, KPX_ERR_INVALID_ARGUMENT if a block id outside
- * [0, layout.num_blocks) was met -- and clears it.  No reference counterpart (the
- * reference does not check its launches on the hot path). */
+ * [0, layout.num_blocks) was met -- and clears it.  After KPX_ERR_DEVICE_TIMEOUT the launch
+ * that raised it has left rows of its output unwritten and piece counters in the workspace
+ * half counted, so the workspace has to start over before its next launch.
+ * kpx_workspace_status does that itself when it reads this code (it wipes the workspace to the
+ * size kpx_workspace_init was given); a caller that watches the word by other means calls
+ * kpx_workspace_init again.  Then repeat the step.  No reference counterpart (the reference does not check its launches on the hot
+ * path; its only recovery is the eager fallback after a failed graph capture,
+ * kuiper/source/model/qwen_base.cpp:754). */
 KPX_API int kpx_workspace_init(void* workspace, int64_t workspace_bytes, void* stream);
 KPX_API int kpx_workspace_status(void* workspace, void* stream);
 

@@ -18,6 +18,10 @@ struct CudaConfig {
   bool use_cuda_graph = false;
   void* kv_workspace = nullptr;  // zero-initialised scratch for kpx_paged_prefill / kpx_paged_decode
   size_t kv_workspace_bytes = 0;
+  // The kernel::*_cu free functions return void, as the reference's do; a library status other
+  // than KPX_OK that one of them met is kept here (the first since the last take_status()), so
+  // that the layer's forward() can hand it to the model instead of going on with stale data.
+  int last_status = KPX_OK;
 
   CudaConfig() = default;
   ~CudaConfig() {
@@ -30,6 +34,15 @@ struct CudaConfig {
   void init(bool enable_graph = false) {
     if (!stream) cudaStreamCreate(&stream);
     use_cuda_graph = enable_graph;
+  }
+
+  void note_status(int rc) {
+    if (rc != KPX_OK && last_status == KPX_OK) last_status = rc;
+  }
+  int take_status() {
+    const int rc = last_status;
+    last_status = KPX_OK;
+    return rc;
   }
 
   // Make sure the scratch holds `bytes`; (re)allocation synchronises the device, so size it

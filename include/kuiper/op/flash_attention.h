@@ -48,7 +48,7 @@ class FlashAttentionDecodeLayer : public Layer {
       kernel::flash_attention_decode_fp16_gpu_pos_cu(get_input(4).ptr<int32_t>(), head_num_, kv_head_num_, head_size_,
                                                      kv_mul_, layer_index_, seq_len_, kv_dim_, get_input(0),
                                                      get_input(1), get_input(2), get_input(3), cuda_config_.get());
-      return base::error::Success();
+      return kernel::detail::taken_status(cuda_config_.get());
     }
     return forward(pos_, head_num_, kv_head_num_, head_size_, kv_mul_, layer_index_, seq_len_, kv_dim_,
                    get_input(0), get_input(1), get_input(2), get_input(3));
@@ -60,7 +60,7 @@ class FlashAttentionDecodeLayer : public Layer {
                        const tensor::Tensor& val_cache) {
     kernel::flash_attention_decode_cu(pos, head_num, kv_head_num, head_size, kv_mul, layer_idx, seq_len, kv_dim,
                                       query, mha_output, key_cache, val_cache, cuda_config_.get());
-    return base::error::Success();
+    return kernel::detail::taken_status(cuda_config_.get());
   }
 
   void set_layer_index(int32_t layer_index) { layer_index_ = layer_index; }
@@ -134,7 +134,7 @@ class FlashAttentionPrefillLayer : public Layer {
     if (!cuda_config_) return base::error::InvalidArgument("prefill needs a CudaConfig (it owns the scratch)");
     kernel::flash_attention_prefill_cu(start_pos, seq_len, head_num, kv_head_num, head_size, kv_mul, layer_idx,
                                        max_seq_len, kv_dim, query, output, key_cache, val_cache, cuda_config_.get());
-    return base::error::Success();
+    return kernel::detail::taken_status(cuda_config_.get());
   }
 
   void set_cur_seq_len(int32_t seq_len) { cur_seq_len_ = seq_len; }

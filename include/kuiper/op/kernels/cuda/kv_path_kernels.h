@@ -18,8 +18,33 @@
 
 namespace kernel {
 namespace detail {
-inline void report(int rc, const char* what) {
-  if (rc != KPX_OK) std::fprintf(stderr, "[kuiper-b200] %s: %s\n", what, kpx_status_string(rc));
+inline void report(int rc, const char* what, CudaConfig* config = nullptr) {
+  if (rc == KPX_OK) return;
+  std::fprintf(stderr, "[kuiper-b200] %s: %s\n", what, kpx_status_string(rc));
+  if (config) config->note_status(rc);
+}
+// What the void functions below met since the last look (kept in the CudaConfig), as a Status
+// for the layer's forward() to return.
+inline base::Status taken_status(CudaConfig* config) {
+  const int rc = config ? config->take_status() : KPX_OK;
+  return rc == KPX_OK ? base::error::Success() : base::Status(rc, kpx_status_string(rc));
+}
+// Single-query attention through the library.  First choice is the entry point with built-in
+// scratch (nothing to allocate, nothing to pass); a head layout beyond its limit (for example
+// 32 KV heads, plain multi-head attention) falls back to kpx_paged_decode with the config's
+// workspace, grown once.  Without a config there is nowhere to keep a workspace and the limit
+// is returned.
+inline int decode_any(void* out, const void* q, const void* k, const void* v, const kpx_kv_layout* lay,
+                      const int32_t* table, int32_t max_blocks, const int32_t* seq_lens, int32_t len_bias,
+                      int32_t batch, int32_t head_num, float scale, CudaConfig* config) {
+  void* stream = config ? config->stream : nullptr;
+  int rc = kpx_paged_decode_static(out, q, k, v, lay, table, max_blocks, seq_lens, len_bias, batch, head_num,
+                                   scale, stream);
+  if (rc != KPX_ERR_STATIC_SCRATCH_LIMIT || !config) return rc;
+  const int64_t need = kpx_decode_workspace_bytes(batch, head_num, lay->num_kv_heads, lay->head_size);
+  if (need < 0 || !config->ensure_kv_workspace(static_cast<size_t>(need))) return KPX_ERR_WORKSPACE_TOO_SMALL;
+  return kpx_paged_decode(out, q, k, v, lay, table, max_blocks, seq_lens, len_bias, batch, head_num, scale,
+                          config->kv_workspace, static_cast<int64_t>(config->kv_workspace_bytes), stream);
 }
 inline int32_t kpx_dtype(const tensor::Tensor& t) {
   switch (t.data_type()) {
@@ -43,13 +68,13 @@ inline uint8_t* layer_base(const tensor::Tensor& cache, int32_t layer_index, int
 inline void decode_contiguous(const int32_t* pos_dev, int32_t host_len, int32_t head_num, int32_t layer_index,
                               int32_t seq_len, int32_t kv_dim, int32_t head_size, const tensor::Tensor& out,
                               const tensor::Tensor& query, const tensor::Tensor& key_cache,
-                              const tensor::Tensor& value_cache, void* stream, const char* what) {
+                              const tensor::Tensor& value_cache, CudaConfig* config, const char* what) {
   kpx_kv_layout lay = contiguous_layout(kpx_dtype(key_cache), kv_dim, head_size);
-  report(kpx_paged_decode_static(const_cast<uint8_t*>(out.ptr<uint8_t>()), query.ptr<uint8_t>(),
-                                 layer_base(key_cache, layer_index, seq_len, kv_dim),
-                                 layer_base(value_cache, layer_index, seq_len, kv_dim), &lay, nullptr, 0,
-                                 pos_dev, pos_dev ? 1 : host_len, 1, head_num,
-                                 1.f / std::sqrt(static_cast<float>(head_size)), stream), what);
+  report(decode_any(const_cast<uint8_t*>(out.ptr<uint8_t>()), query.ptr<uint8_t>(),
+                    layer_base(key_cache, layer_index, seq_len, kv_dim),
+                    layer_base(value_cache, layer_index, seq_len, kv_dim), &lay, nullptr, 0, pos_dev,
+                    pos_dev ? 1 : host_len, 1, head_num, 1.f / std::sqrt(static_cast<float>(head_size)), config),
+         what, config);
 }
 // causal attention of seq_len query rows at start_pos.. over the layer's cache
 inline void prefill_contiguous(int32_t start_pos, int32_t n, int32_t head_num, int32_t layer_index,
@@ -64,7 +89,7 @@ inline void prefill_contiguous(int32_t start_pos, int32_t n, int32_t head_num, i
   kpx_kv_layout lay = contiguous_layout(kpx_dtype(key_cache), kv_dim, head_size);
   const int64_t need = kpx_prefill_workspace_bytes(n, head_num, kv_dim / head_size, head_size);
   if (need < 0 || !config->ensure_kv_workspace(static_cast<size_t>(need))) {
-    report(KPX_ERR_WORKSPACE_TOO_SMALL, what);
+    report(KPX_ERR_WORKSPACE_TOO_SMALL, what, config);
     return;
   }
   const int32_t cu[2] = {0, n};
@@ -73,7 +98,7 @@ inline void prefill_contiguous(int32_t start_pos, int32_t n, int32_t head_num, i
                            layer_base(value_cache, layer_index, max_seq_len, kv_dim), &lay, nullptr, 0, cu,
                            &start_pos, 1, head_num, 1.f / std::sqrt(static_cast<float>(head_size)),
                            config->kv_workspace, static_cast<int64_t>(config->kv_workspace_bytes),
-                           config->stream), what);
+                           config->stream), what, config);
 }
 }  // namespace detail
 
@@ -85,7 +110,7 @@ inline void mha_kernel_cu(int32_t pos, int32_t head_num, int32_t layer_index, in
                           base::DeviceType device_type, CudaConfig* config) {
   UNUSED(kv_mul); UNUSED(score_tensor); UNUSED(device_type);  // scores are never materialised
   detail::decode_contiguous(nullptr, pos + 1, head_num, layer_index, seq_len, kv_dim, head_size, mha_out,
-                            query_tensor, key_cache_tensor, value_cache_tensor, detail::stream_of(config),
+                            query_tensor, key_cache_tensor, value_cache_tensor, config,
                             "mha_kernel_cu");
 }
 inline void mha_kernel_cu_gpu_pos(const int32_t* pos_ptr, int32_t head_num, int32_t layer_index, int32_t seq_len,
@@ -96,7 +121,7 @@ inline void mha_kernel_cu_gpu_pos(const int32_t* pos_ptr, int32_t head_num, int3
                                   CudaConfig* config) {
   UNUSED(kv_mul); UNUSED(score_tensor); UNUSED(device_type);
   detail::decode_contiguous(pos_ptr, 0, head_num, layer_index, seq_len, kv_dim, head_size, mha_out, query_tensor,
-                            key_cache_tensor, value_cache_tensor, detail::stream_of(config),
+                            key_cache_tensor, value_cache_tensor, config,
                             "mha_kernel_cu_gpu_pos");
 }
 inline void batched_mha_kernel_cu(int32_t start_pos, int32_t seq_len, int32_t head_num, int32_t layer_index,
@@ -119,7 +144,7 @@ inline void batched_mha_kernel_cu(int32_t start_pos, int32_t seq_len, int32_t he
                    const tensor::Tensor& value_cache, CudaConfig* config) {                               \
     UNUSED(kv_head_num); UNUSED(kv_mul);                                                                   \
     detail::decode_contiguous(nullptr, pos + 1, head_num, layer_index, max_seq_len, kv_dim, head_size,    \
-                              output, query, key_cache, value_cache, detail::stream_of(config), #name);   \
+                              output, query, key_cache, value_cache, config, #name);                      \
   }
 #define KUIPER_B200_DECODE_GPU_POS_CU(name)                                                                \
   inline void name(const int32_t* pos_ptr, int32_t head_num, int32_t kv_head_num, int32_t head_size,      \
@@ -129,7 +154,7 @@ inline void batched_mha_kernel_cu(int32_t start_pos, int32_t seq_len, int32_t he
                    CudaConfig* config) {                                                                   \
     UNUSED(kv_head_num); UNUSED(kv_mul);                                                                   \
     detail::decode_contiguous(pos_ptr, 0, head_num, layer_index, max_seq_len, kv_dim, head_size, output,  \
-                              query, key_cache, value_cache, detail::stream_of(config), #name);           \
+                              query, key_cache, value_cache, config, #name);                              \
   }
 #define KUIPER_B200_PREFILL_CU(name)                                                                       \
   inline void name(int32_t start_pos, int32_t seq_len, int32_t head_num, int32_t kv_head_num,             \

@@ -63,7 +63,7 @@ class MultiHeadAttention : public op::Layer {
       kernel::get_mha_kernel(device_type_)(pos_, head_num_, layer_index_, seq_len_, kv_dim_, kv_mul_, head_size_,
                                            get_output(0), get_input(0), get_input(1), get_input(2), get_input(3),
                                            device_type_, cuda_config_ ? cuda_config_.get() : nullptr);
-      return base::error::Success();
+      return kernel::detail::taken_status(cuda_config_.get());
     }
     return paged_decode(get_input(0), get_output(0), get_input(2), get_input(3), head_num_, kv_dim_ / head_size_,
                         head_size_, paged_, cuda_config_.get());
@@ -78,11 +78,12 @@ class MultiHeadAttention : public op::Layer {
     int rc = kpx_layout_paged(&lay, kernel::detail::kpx_dtype(k_pool), kv_heads, head_size, 16);
     if (rc != KPX_OK) return base::Status(rc, kpx_status_string(rc));
     lay.num_blocks = pa.num_blocks;
-    rc = kpx_paged_decode_static(const_cast<uint8_t*>(out.ptr<uint8_t>()), query.ptr<uint8_t>(),
-                                 k_pool.ptr<uint8_t>(), v_pool.ptr<uint8_t>(), &lay,
-                                 pa.block_table.ptr<int32_t>(), pa.block_table.get_dim(pa.block_table.dims_size() - 1),
-                                 pa.seq_lens.ptr<int32_t>(), 0, pa.batch, head_num,
-                                 1.f / std::sqrt(static_cast<float>(head_size)), config ? config->stream : nullptr);
+    rc = kernel::detail::decode_any(const_cast<uint8_t*>(out.ptr<uint8_t>()), query.ptr<uint8_t>(),
+                                    k_pool.ptr<uint8_t>(), v_pool.ptr<uint8_t>(), &lay,
+                                    pa.block_table.ptr<int32_t>(),
+                                    pa.block_table.get_dim(pa.block_table.dims_size() - 1),
+                                    pa.seq_lens.ptr<int32_t>(), 0, pa.batch, head_num,
+                                    1.f / std::sqrt(static_cast<float>(head_size)), config);
     return rc == KPX_OK ? base::error::Success() : base::Status(rc, kpx_status_string(rc));
   }
 

@@ -38,7 +38,7 @@ class MHAGpuPosLayer : public Layer {
                        const tensor::Tensor& val_cache) {
     kernel::mha_kernel_cu_gpu_pos(pos_ptr, head_num, layer_idx, seq_len, kv_dim, kv_mul, head_size, mha_output, query,
                                   score_storage, key_cache, val_cache, device_type_, cuda_config_.get());
-    return base::error::Success();
+    return kernel::detail::taken_status(cuda_config_.get());
   }
 };
 
@@ -52,7 +52,7 @@ class BatchedMHALayer : public Layer {
     kernel::batched_mha_kernel_cu(start_pos, seq_len, head_num, layer_idx, max_seq_len, dim, kv_dim, kv_mul,
                                   head_size, mha_output, query, score_storage, key_cache, val_cache, device_type_,
                                   cuda_config_.get());
-    return base::error::Success();
+    return kernel::detail::taken_status(cuda_config_.get());
   }
 };
 
@@ -94,7 +94,7 @@ class FlashAttentionDecodeGpuPosLayer : public Layer {
     kernel::flash_attention_decode_fp16_gpu_pos_cu(pos_gpu, head_num, kv_head_num, head_size, kv_mul, layer_idx,
                                                    seq_len, kv_dim, query, mha_output, key_cache, val_cache,
                                                    cuda_config_.get());
-    return base::error::Success();
+    return kernel::detail::taken_status(cuda_config_.get());
   }
 
  private:

@@ -57,6 +57,8 @@ SIGNATURES = {
     "kpx_decode_workspace_bytes": (_I64, [_I32, _I32, _I32, _I32]),
     "kpx_paged_decode": (C.c_int, [_P, _P, _P, _P, _LP, _P, _I32, _P, _I32, _I32, _I32, _F32,
                                    _P, _I64, _P]),
+    "kpx_paged_decode_overlapped": (C.c_int, [_P, _P, _P, _P, _LP, _P, _I32, _P, _I32, _I32, _I32, _F32,
+                                              _P, _I64, _P]),
     "kpx_rope_append_decode": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _LP, _P, _I32, _P, _I32, _I32, _F32,
                                          _P, _I64, _I32, _P]),
     "kpx_paged_decode_static": (C.c_int, [_P, _P, _P, _P, _LP, _P, _I32, _P, _I32, _I32, _I32, _F32, _P]),
@@ -209,6 +211,16 @@ def rope_append_decode(out, q, k_new, v_new, sin_cache, cos_cache, k_pool, v_poo
                                        ptr(block_table), max_blocks_per_seq, ptr(positions), batch,
                                        num_q_heads, scale, ptr(workspace), workspace_bytes, flags,
                                        _stream(stream)), "kpx_rope_append_decode")
+
+
+def paged_decode_overlapped(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq, seq_lens,
+                            len_bias, batch, num_q_heads, scale, workspace, workspace_bytes,
+                            stream=None) -> None:
+    """kpx_paged_decode in the form for launches that overlap on the GPU (own workspace each)."""
+    check(lib().kpx_paged_decode_overlapped(ptr(out), ptr(q), ptr(k_pool), ptr(v_pool), C.byref(layout),
+                                            ptr(block_table), max_blocks_per_seq, ptr(seq_lens), len_bias,
+                                            batch, num_q_heads, scale, ptr(workspace), workspace_bytes,
+                                            _stream(stream)), "kpx_paged_decode_overlapped")
 
 
 def paged_decode_static(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq, seq_lens,

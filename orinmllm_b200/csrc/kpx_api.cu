@@ -96,18 +96,39 @@ extern "C" int kpx_layout_contiguous(kpx_kv_layout* out, int32_t dtype, int32_t 
   return KPX_OK;
 }
 
-extern "C" int kpx_workspace_init(void* workspace, int64_t workspace_bytes, void* stream) {
-  if (!workspace || workspace_bytes < 256) return KPX_ERR_INVALID_ARGUMENT;
-  KPX_CUDA_TRY(cudaMemsetAsync(workspace, 0, size_t(workspace_bytes), static_cast<cudaStream_t>(stream)));
+namespace {
+// Header of a workspace: word 0 = sticky status (the kernels raise it), bytes 8..15 = the size
+// kpx_workspace_init was given, so that the workspace can be wiped again without asking.
+__global__ void workspace_note_size(int64_t* header, int64_t bytes) { header[1] = bytes; }
+
+int wipe_workspace(void* workspace, int64_t workspace_bytes, cudaStream_t s) {
+  KPX_CUDA_TRY(cudaMemsetAsync(workspace, 0, size_t(workspace_bytes), s));
+  workspace_note_size<<<1, 1, 0, s>>>(static_cast<int64_t*>(workspace), workspace_bytes);
+  KPX_CUDA_TRY(cudaGetLastError());
   return KPX_OK;
+}
+}  // namespace
+
+extern "C" int kpx_workspace_init(void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!workspace || workspace_bytes < 256 || (reinterpret_cast<uintptr_t>(workspace) & 15))
+    return KPX_ERR_INVALID_ARGUMENT;
+  return wipe_workspace(workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int kpx_workspace_status(void* workspace, void* stream) {
-  if (!workspace) return KPX_ERR_INVALID_ARGUMENT;
-  int32_t st = 0;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15)) return KPX_ERR_INVALID_ARGUMENT;
+  int64_t header[2] = {0, 0};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  KPX_CUDA_TRY(cudaMemcpyAsync(&st, workspace, sizeof(st), cudaMemcpyDeviceToHost, s));
+  KPX_CUDA_TRY(cudaMemcpyAsync(header, workspace, sizeof(header), cudaMemcpyDeviceToHost, s));
   KPX_CUDA_TRY(cudaStreamSynchronize(s));
-  if (st != 0) KPX_CUDA_TRY(cudaMemsetAsync(workspace, 0, sizeof(st), s));
+  const int32_t st = static_cast<int32_t>(header[0] & 0xffffffff);
+  if (st == KPX_ERR_DEVICE_TIMEOUT && header[1] >= 256) {
+    // warps that gave up never counted their pieces: the counters in the workspace are stale and
+    // the next launch would assemble at the wrong count, so the whole workspace starts over
+    int rc = wipe_workspace(workspace, header[1], s);
+    if (rc != KPX_OK) return rc;
+  } else if (st != 0) {
+    KPX_CUDA_TRY(cudaMemsetAsync(workspace, 0, sizeof(int32_t), s));
+  }
   return st;
 }

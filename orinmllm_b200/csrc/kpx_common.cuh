@@ -97,8 +97,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait: returns false after kWaitLimit failed polls (each poll may itself
 // block for a hardware-defined time slice) instead of spinning forever.
 constexpr uint32_t kWaitLimit = 1u << 22;
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = kWaitLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 64) __nanosleep(64);
   }

@@ -1,5 +1,7 @@
 // Entry points of the paged GQA decode attention (kernel and launch forms: kpx_decode_impl.cuh;
 // the kernels themselves are instantiated per element type in kpx_decode_{f16,bf16,f32}.cu).
+#include <climits>
+
 #include "kpx_decode_impl.cuh"
 
 namespace kpx {
@@ -10,6 +12,9 @@ int g_decode_variant = 0;
 // is below g_small_below blocks per warp of the grid; then ranges hold at least
 // g_min_blocks_per_range blocks while at least g_min_warps_per_sm warps per SM stay active.
 int g_small_below = 12, g_min_blocks_per_range = 12, g_min_warps_per_sm = 4;
+// Test-only: polls before a bounded wait gives up, and the warp whose first tile never comes.
+uint32_t g_wait_limit = kWaitLimit;
+int g_withhold_worker = -1;
 }  // namespace decode
 }  // namespace kpx
 
@@ -24,6 +29,14 @@ extern "C" __attribute__((visibility("default"))) void kpx_internal_set_decode_s
   g_small_below = below;
   if (min_blocks > 0) g_min_blocks_per_range = min_blocks;
   if (min_warps >= 0) g_min_warps_per_sm = min_warps;
+}
+
+// Not in the header: lets a test make a bounded wait run out (the tile request of one warp is
+// announced but never issued; every other warp finishes) without a faulting or endless kernel.
+extern "C" __attribute__((visibility("default"))) void kpx_internal_set_decode_fault(uint32_t wait_limit,
+                                                                                       int withhold_worker) {
+  g_wait_limit = wait_limit ? wait_limit : kWaitLimit;
+  g_withhold_worker = withhold_worker;
 }
 
 extern "C" int64_t kpx_decode_workspace_bytes(int32_t batch, int32_t num_q_heads,
@@ -45,6 +58,16 @@ extern "C" int kpx_paged_decode(void* out, const void* q, const void* k_pool, co
   return kpx::decode_rows(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq, nullptr,
                           seq_lens, len_bias, batch, num_q_heads, scale, workspace, workspace_bytes,
                           stream);
+}
+
+extern "C" int kpx_paged_decode_overlapped(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                           const kpx_kv_layout* layout, const int32_t* block_table,
+                                           int32_t max_blocks_per_seq, const int32_t* seq_lens,
+                                           int32_t len_bias, int32_t batch, int32_t num_q_heads, float scale,
+                                           void* workspace, int64_t workspace_bytes, void* stream) {
+  return kpx::decode_rows(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq, nullptr,
+                          seq_lens, len_bias, batch, num_q_heads, scale, workspace, workspace_bytes,
+                          stream, nullptr, KPX_DECODE_OVERLAPPED);
 }
 
 extern "C" int kpx_rope_append_decode(void* out, const void* q, const void* k_new, const void* v_new,
@@ -78,6 +101,8 @@ int kpx::decode_rows(void* out, const void* q, const void* k_pool, const void* v
   if (num_q_heads / layout->num_kv_heads > 64) return KPX_ERR_UNIMPLEMENTED;
   if (block_table && max_blocks_per_seq <= 0) return KPX_ERR_INVALID_ARGUMENT;
   if (!seq_lens && len_bias < 0) return KPX_ERR_INVALID_ARGUMENT;
+  if (!seq_lens && block_table && int64_t(len_bias) > int64_t(max_blocks_per_seq) * kBS)
+    return KPX_ERR_INVALID_ARGUMENT;  // a fixed length the table rows cannot hold
   if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15)) return KPX_ERR_INVALID_ARGUMENT;
   if ((reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool) |
        reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 15)
@@ -107,6 +132,11 @@ int kpx::decode_rows(void* out, const void* q, const void* k_pool, const void* v
   p.token_stride_b = layout->token_stride * eb;
   p.num_blocks = layout->num_blocks;
   p.max_blocks_per_seq = max_blocks_per_seq;
+  // the fused step stores its new token at position len: the row must hold one more
+  {
+    const int64_t row_tokens = int64_t(max_blocks_per_seq) * kBS - (fused ? 1 : 0);
+    p.max_cached_tokens = block_table ? int32_t(row_tokens > INT32_MAX ? INT32_MAX : row_tokens) : 0;
+  }
   p.len_bias = len_bias;
   p.num_q_heads = num_q_heads;
   p.num_kv_heads = layout->num_kv_heads;
@@ -116,7 +146,8 @@ int kpx::decode_rows(void* out, const void* q, const void* k_pool, const void* v
   p.tile_contig = tile_contiguous(layout) ? 1 : 0;
   p.min_blocks_per_range = g_min_blocks_per_range;
   p.min_warps_per_sm = g_min_warps_per_sm;
-  p.debug = g_decode_variant & ~3;
+  p.wait_limit = g_wait_limit;
+  p.withhold_worker = g_withhold_worker;
   p.qscale = scale * kLog2e;
   // the block prefix of one launch lives in shared memory: long batches go in slices
   for (int32_t b0 = 0; b0 < batch; b0 += kMaxBatch) {

@@ -40,7 +40,7 @@ namespace decode {
 
 constexpr int kD = 128;          // head size
 constexpr int kBS = 16;          // tokens per block
-constexpr int kMaxBatch = 1024;  // sequences per launch (their block prefix lives in smem)
+constexpr int kMaxBatch = 512;   // sequences per launch (their block prefix lives in smem)
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct DecodeParams {
@@ -66,12 +66,16 @@ struct DecodeParams {
   int64_t block_stride_b, head_stride_b, token_stride_b;  // bytes
   int64_t num_blocks;
   int32_t max_blocks_per_seq, len_bias, batch;
+  int32_t max_cached_tokens;  // most tokens a table row can address from the pool
   int32_t num_q_heads, num_kv_heads, kv_mul;
   int32_t head_groups;  // ceil(kv_mul / QH)
   int32_t partial_slots;  // slots of kPartialFloats floats in `partials`
   int32_t tile_contig;
   int32_t min_blocks_per_range, min_warps_per_sm;  // read by the small-launch form of the kernel only
-  int32_t debug;  // EXPERIMENT: timing-only switches
+  // Polls a bounded wait makes before it gives up (kWaitLimit), and, for the test of that path
+  // only, the warp whose first tile request is announced to its barrier but never issued (-1: none).
+  uint32_t wait_limit;
+  int32_t withhold_worker;
   float qscale;  // softmax scale * log2(e)
 };
 
@@ -86,13 +90,21 @@ struct Cfg {
   static constexpr int kOffPrefix = kOffBars + kWarps * 2 * NS * 8;
   static constexpr int kOffP = kOffPrefix + (kMaxBatch + 1) * 4 + 12;
   static constexpr int kSmem = kOffP + kWarps * 2 * kBS * 4 * 4;  // two weight buffers per warp
+  // Fused step only: per warp, the rotated query rows of the item's QH heads, the new token's
+  // rotated K row and its V row (all of type T), and the id of the block the token goes to.
+  static constexpr int kStageB = (QH + 2) * kD * kEltB + 16;
+  static constexpr int kSmemFused = kSmem + kWarps * kStageB;
   // one workspace slot: QH accumulators of 128, then QH maxima, QH sums; padded so that
   // every slot starts on a 16-byte boundary (the assembling warp reads float4)
   static constexpr int kPartialFloats = QH * kD + 8;
 };
 
+// Tokens of sequence b that lie in the pool.  A length read from device memory that would reach
+// past the sequence's table row is cut to the row (and reported by the prologue): the table is
+// never read out of bounds.
 __device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
   int len = (p.seq_lens ? p.seq_lens[b] : 0) + p.len_bias;
+  if (p.block_table && len > p.max_cached_tokens) len = p.max_cached_tokens;
   return len < 0 ? 0 : len;
 }
 __device__ __forceinline__ int blocks_of(int len) { return (len + kBS - 1) / kBS; }
@@ -159,21 +171,47 @@ __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// One 16-byte chunk of a head row after the half-split rotation: `lo` / `hi` hold the elements
-// j0..j0+E-1 and 64+j0.. of the row, sn / cs the table entries of those pairs; the result is the
-// rotated value of the lower (upper = false) or upper half, with the two products rounded
-// separately and one rounding to T, exactly as rope_append_kernel stores it.
-template <typename T, int E>
-__device__ __forceinline__ void rotate_chunk(const uint4& lo_raw, const uint4& hi_raw, const float* sn,
-                                             const float* cs, bool upper, float* out) {
-  float lo[E], hi[E];
-  Elt<T>::unpack(lo_raw, lo);
-  Elt<T>::unpack(hi_raw, hi);
+// Fused step, start of an item: rotates the new token's query rows of the item's QH heads at
+// position `pos` and leaves them, rounded to T, in the warp's staging area; with `with_kv` (the
+// warp's segment reaches the end of the item, so it will also account for the new token) the
+// rotated K row, the V row and the id of the block that takes the token follow.  Half-split
+// pairs (j, j + 64), sin/cos read at pos*128 + 2j, products rounded separately and one rounding
+// to T: the bits rope_append_kernel stores.  Kept out of line so that the streaming loop's
+// register allocation is that of the plain kernel; the caller brackets it with __syncwarp().
+template <typename T, int QH>
+__device__ __noinline__ void stage_new_token(const T* q_kv_group, int hg, int kv_mul, const T* k_row,
+                                             const uint8_t* v_row, bool with_kv, const float* sin_row,
+                                             const float* cos_row, const int32_t* table_entry,
+                                             int identity_id, uint8_t* stage, int lane) {
+  constexpr int E = Elt<T>::kPer16B;
+  constexpr int G = kD / 2 / E;  // 16-byte pair groups per row
+  constexpr int kRowB = kD * int(sizeof(T));
+  const int rows = QH + (with_kv ? 1 : 0);
+  for (int task = lane; task < rows * G; task += 32) {
+    const int r = task / G, g = task - r * G;
+    const int hq = hg * QH + r;
+    const T* src = r < QH ? q_kv_group + (hq < kv_mul ? hq : 0) * kD : k_row;
+    float lo[E], hi[E];
+    Elt<T>::unpack(__ldg(reinterpret_cast<const uint4*>(src + g * E)), lo);
+    Elt<T>::unpack(__ldg(reinterpret_cast<const uint4*>(src + kD / 2 + g * E)), hi);
+    __align__(16) T lo_out[E];
+    __align__(16) T hi_out[E];
 #pragma unroll
-  for (int e = 0; e < E; ++e) {
-    const float r = upper ? __fadd_rn(__fmul_rn(lo[e], sn[e]), __fmul_rn(hi[e], cs[e]))
-                          : __fsub_rn(__fmul_rn(lo[e], cs[e]), __fmul_rn(hi[e], sn[e]));
-    out[e] = Elt<T>::to_float(Elt<T>::from_float(r));
+    for (int e = 0; e < E; ++e) {
+      const float sn = __ldg(sin_row + 2 * (g * E + e)), cs = __ldg(cos_row + 2 * (g * E + e));
+      lo_out[e] = Elt<T>::from_float(__fsub_rn(__fmul_rn(lo[e], cs), __fmul_rn(hi[e], sn)));
+      hi_out[e] = Elt<T>::from_float(__fadd_rn(__fmul_rn(lo[e], sn), __fmul_rn(hi[e], cs)));
+    }
+    uint8_t* dst = stage + r * kRowB;
+    *reinterpret_cast<uint4*>(dst + g * 16) = *reinterpret_cast<const uint4*>(lo_out);
+    *reinterpret_cast<uint4*>(dst + kRowB / 2 + g * 16) = *reinterpret_cast<const uint4*>(hi_out);
+  }
+  if (with_kv) {
+    for (int task = lane; task < kRowB / 16; task += 32)
+      *reinterpret_cast<uint4*>(stage + (QH + 1) * kRowB + task * 16) =
+          __ldg(reinterpret_cast<const uint4*>(v_row) + task);
+    if (lane == 0)
+      *reinterpret_cast<int32_t*>(stage + (QH + 2) * kRowB) = table_entry ? __ldg(table_entry) : identity_id;
   }
 }
 
@@ -200,6 +238,7 @@ paged_decode_kernel(const DecodeParams p) {
   int* prefix = reinterpret_cast<int*>(smem + C::kOffPrefix);
   uint8_t* ring = smem + warp * C::kWarpRingB;
   float* p_s = reinterpret_cast<float*>(smem + C::kOffP) + warp * (2 * kBS * 4);  // two buffers
+  uint8_t* stage = smem + C::kSmem + warp * C::kStageB;  // fused step only
 
   // ---- prologue: block prefix over sequences (whole CTA), this warp's barriers ----
   if (lane == 0) {
@@ -207,7 +246,11 @@ paged_decode_kernel(const DecodeParams p) {
     for (int s = 0; s < 2 * NS; ++s) mbar_init(bars + s, 1);
     mbar_fence_init();
   }
-  for (int b = tid; b < p.batch; b += C::kThreads) prefix[b + 1] = blocks_of(seq_len_of(p, b));
+  for (int b = tid; b < p.batch; b += C::kThreads) {
+    prefix[b + 1] = blocks_of(seq_len_of(p, b));
+    if (p.block_table && p.seq_lens && blockIdx.x == 0 && p.seq_lens[b] + p.len_bias > p.max_cached_tokens)
+      atomicMax(p.status, KPX_ERR_INVALID_ARGUMENT);
+  }
   if (tid == 0) prefix[0] = 0;
   __syncthreads();
   if (warp == 0) {  // inclusive scan in chunks of 32
@@ -310,13 +353,13 @@ paged_decode_kernel(const DecodeParams p) {
     return id;
   };
   // request one tile (callers have __syncwarp'ed after the last read of the slot)
-  auto copy_tile = [&](const uint8_t* pool, int64_t off, int rows, int slot_index) {
+  auto copy_tile = [&](const uint8_t* pool, int64_t off, int rows, int slot_index, bool withhold = false) {
     uint64_t* bar = bars + slot_index;
     uint8_t* dst = ring + slot_index * C::kTileB;
     if (p.tile_contig) {
       if (lane == 0) {
         mbar_arrive_expect_tx(bar, C::kTileB);
-        bulk_g2s(dst, pool + off, C::kTileB, bar);
+        if (!withhold) bulk_g2s(dst, pool + off, C::kTileB, bar);
       }
     } else {
       // strided rows (the reference's token-major cache): one bulk copy per existing row
@@ -329,7 +372,7 @@ paged_decode_kernel(const DecodeParams p) {
   auto issue_k = [&](int slot) {  // K tile of the block at pc; then step pc
     last_off = int64_t(pc_id) * p.block_stride_b + int64_t(pc.kvh) * p.head_stride_b;
     last_rows = min(kBS, pc.len - pc.blk * kBS);
-    copy_tile(p.k_pool, last_off, last_rows, slot);
+    copy_tile(p.k_pool, last_off, last_rows, slot, k_issued == 0 && worker == p.withhold_worker);
     ++k_issued;
     pc.advance(p, prefix);
     if (k_issued < n) pc_id = load_id();
@@ -354,9 +397,22 @@ paged_decode_kernel(const DecodeParams p) {
   float2 acc[QH][HP];
   float m_run[NV], l_run[NV];
 
-  auto begin_item = [&]() {
+  // blocks_left: blocks of the warp's range from the item's first block in it onwards
+  auto begin_item = [&](int blocks_left) {
     const int hg = cur.sub - cur.kvh * p.head_groups;
     const T* qrow = static_cast<const T*>(p.q) + int64_t(cur.b) * p.num_q_heads * kD;
+    if constexpr (kFused) {
+      const int seg = min(blocks_left, cur.nblk - cur.blk);
+      const bool ends_item = cur.blk + seg == cur.nblk;
+      __syncwarp();  // the previous item's readers of the staging area are done
+      stage_new_token<T, QH>(
+          qrow + int64_t(cur.kvh) * p.kv_mul * kD, hg, p.kv_mul,
+          static_cast<const T*>(p.k_new) + (int64_t(cur.b) * p.num_kv_heads + cur.kvh) * kD,
+          static_cast<const uint8_t*>(p.v_new) + (int64_t(cur.b) * p.num_kv_heads + cur.kvh) * (kD * C::kEltB),
+          ends_item, p.sin_cache + int64_t(cur.len) * kD, p.cos_cache + int64_t(cur.len) * kD,
+          cur.row ? cur.row + cur.len / kBS : nullptr, cur.len / kBS, stage, lane);
+      __syncwarp();
+    }
 #pragma unroll
     for (int j = 0; j < QH; ++j) {
       const int hq = hg * QH + j;
@@ -366,22 +422,12 @@ paged_decode_kernel(const DecodeParams p) {
 #pragma unroll
       for (int c = 0; c < NCH; ++c) {
         float f[E];
-        if (kFused && !(p.debug & 8)) {
-          // fused step: rotate the query at the new token's position (= cached length)
-          const int d0 = coff[c] / C::kEltB, j0 = d0 & (kD / 2 - 1);
-          float sn[E], cs[E];
-#pragma unroll
-          for (int e = 0; e < E; ++e) {
-            sn[e] = __ldg(p.sin_cache + int64_t(cur.len) * kD + 2 * (j0 + e));
-            cs[e] = __ldg(p.cos_cache + int64_t(cur.len) * kD + 2 * (j0 + e));
-          }
-          const uint4 lo = __ldg(reinterpret_cast<const uint4*>(qh + j0));
-          const uint4 hi = __ldg(reinterpret_cast<const uint4*>(qh + kD / 2 + j0));
-          rotate_chunk<T, E>(lo, hi, sn, cs, d0 >= kD / 2, f);
-        } else {
-          uint4 raw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(qh) + coff[c]));
-          Elt<T>::unpack(raw, f);
-        }
+        uint4 raw;
+        if constexpr (kFused)  // rotated at the new token's position, rounded to T
+          raw = *reinterpret_cast<const uint4*>(stage + j * (kD * C::kEltB) + coff[c]);
+        else
+          raw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(qh) + coff[c]));
+        Elt<T>::unpack(raw, f);
 #pragma unroll
         for (int e = 0; e < E; e += 2)
           q2[j][(c * E + e) / 2] = make_float2(f[e] * sc, f[e + 1] * sc);
@@ -469,32 +515,18 @@ paged_decode_kernel(const DecodeParams p) {
       mh[0] = m_run[0];
       lh[0] = l_run[0];
     }
-    if (kFused && has_item_end && !(p.debug & 4)) {
+    if (kFused && has_item_end) {
       // Fused step: this piece ends the item, so it also carries the new token (position
-      // item.len, not in the pool yet).  Its rotated K row and its V row come from the
-      // caller's rows; every token group computes the same update for its dims.
-      const T* kn = static_cast<const T*>(p.k_new) + (int64_t(item.b) * p.num_kv_heads + item.kvh) * kD;
-      const uint8_t* vn = static_cast<const uint8_t*>(p.v_new) +
-                          (int64_t(item.b) * p.num_kv_heads + item.kvh) * (kD * C::kEltB);
+      // item.len, not in the pool yet).  Its rotated K row and its V row were staged when the
+      // item began; every token group computes the same update for its dims.
+      constexpr int kRowB = kD * C::kEltB;
       float kr[DPT], vf[DPT];
       uint4 kraw[NCH], vraw[NCH];
 #pragma unroll
       for (int c = 0; c < NCH; ++c) {
-        const int d0 = coff[c] / C::kEltB, j0 = d0 & (kD / 2 - 1);
-        float sn[E], cs[E];
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-          sn[e] = __ldg(p.sin_cache + int64_t(item.len) * kD + 2 * (j0 + e));
-          cs[e] = __ldg(p.cos_cache + int64_t(item.len) * kD + 2 * (j0 + e));
-        }
-        const uint4 lo = __ldg(reinterpret_cast<const uint4*>(kn + j0));
-        const uint4 hi = __ldg(reinterpret_cast<const uint4*>(kn + kD / 2 + j0));
-        rotate_chunk<T, E>(lo, hi, sn, cs, d0 >= kD / 2, kr + c * E);
-        __align__(16) T tmp[E];
-#pragma unroll
-        for (int e = 0; e < E; ++e) tmp[e] = Elt<T>::from_float(kr[c * E + e]);
-        kraw[c] = *reinterpret_cast<const uint4*>(tmp);
-        vraw[c] = __ldg(reinterpret_cast<const uint4*>(vn + coff[c]));
+        kraw[c] = *reinterpret_cast<const uint4*>(stage + QH * kRowB + coff[c]);
+        vraw[c] = *reinterpret_cast<const uint4*>(stage + (QH + 1) * kRowB + coff[c]);
+        Elt<T>::unpack(kraw[c], kr + c * E);
         Elt<T>::unpack(vraw[c], vf + c * E);
       }
 #pragma unroll
@@ -517,7 +549,7 @@ paged_decode_kernel(const DecodeParams p) {
       // append: the first head group's warp stores the rows (token group 0 the K row, the last
       // token group the V row) into the block that holds position item.len
       if (hg == 0 && (tg == 0 || tg == TG - 1)) {
-        int id = item.row ? __ldg(item.row + item.len / kBS) : item.len / kBS;
+        const int id = *reinterpret_cast<const int32_t*>(stage + (QH + 2) * kRowB);
         if (id < 0 || (p.num_blocks > 0 && id >= p.num_blocks)) {
           if (sub == 0) atomicMax(p.status, KPX_ERR_INVALID_ARGUMENT);
         } else {
@@ -722,15 +754,19 @@ paged_decode_kernel(const DecodeParams p) {
 
   auto wait_slot = [&](uint64_t* bar, uint32_t ph) -> bool {
     if (mbar_try_wait(bar, ph)) return true;
-    bool ok = mbar_wait_bounded(bar, ph);
+    bool ok = mbar_wait_bounded(bar, ph, p.wait_limit);
     if (!__all_sync(0xffffffffu, ok)) {
+      // Give up: report, then let the tile copies this warp still has in flight land (a bounded
+      // pause far longer than a copy takes) before the warp retires, so that nothing arrives in
+      // shared memory that has passed to another CTA.
       if (lane == 0) atomicMax(p.status, KPX_ERR_DEVICE_TIMEOUT);
+      for (int k = 0; k < 64; ++k) __nanosleep(1000);
       return false;
     }
     return true;
   };
 
-  begin_item();
+  begin_item(n);
   int64_t item_first = u0 - cur.blk;  // global block index where the current item starts
   int ks = 0, vs = 0;                 // slots of the next K block and the next V block to consume
   uint32_t kph = 0, vph = 0;          // their phase parities
@@ -864,6 +900,23 @@ paged_decode_kernel(const DecodeParams p) {
                           (lane & 1) * (kD * C::kEltB / 2);
       asm volatile("prefetch.global.L2 [%0];" ::"l"(qn));
     }
+    if constexpr (kFused) {
+      if (i + m < n && lane >= 8 && lane < 20) {
+        // ... and the rows the fused step rotates with: the new token's K and V rows (two
+        // 128-byte lines each for 16-bit elements) and the sin / cos rows of its position
+        Cursor nx = cur;
+        nx.blk += m - 1;
+        nx.advance(p, prefix);
+        const int64_t kv_row = (int64_t(nx.b) * p.num_kv_heads + nx.kvh) * (kD * C::kEltB);
+        const int l = lane - 8;
+        const uint8_t* src =
+            l < 2   ? static_cast<const uint8_t*>(p.k_new) + kv_row + l * (kD * C::kEltB / 2)
+            : l < 4 ? static_cast<const uint8_t*>(p.v_new) + kv_row + (l - 2) * (kD * C::kEltB / 2)
+            : l < 8 ? reinterpret_cast<const uint8_t*>(p.sin_cache + int64_t(nx.len) * kD) + (l - 4) * 128
+                    : reinterpret_cast<const uint8_t*>(p.cos_cache + int64_t(nx.len) * kD) + (l - 8) * 128;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
+      }
+    }
     const bool to_item_end = (cur.blk + m == cur.nblk);
     const int tail_valid = to_item_end ? cur.len - (cur.nblk - 1) * kBS : kBS;  // tokens in the segment's last block
     if (!step(i, m == 1 ? tail_valid : kBS, std::false_type{})) return;
@@ -885,7 +938,7 @@ paged_decode_kernel(const DecodeParams p) {
       cur.blk += m - 1;
       cur.advance(p, prefix);
       item_first = item_end;
-      begin_item();
+      begin_item(n - i);
     }
   }
 }
@@ -913,6 +966,8 @@ extern int g_decode_variant;
 // is below g_small_below blocks per warp of the grid; then ranges hold at least
 // g_min_blocks_per_range blocks while at least g_min_warps_per_sm warps per SM stay active.
 extern int g_small_below, g_min_blocks_per_range, g_min_warps_per_sm;
+extern uint32_t g_wait_limit;
+extern int g_withhold_worker;
 
 // True when the launch certainly has fewer than g_small_below blocks per warp.
 inline bool small_launch(const DecodeParams& p, int qh, int warps_per_cta) {
@@ -929,20 +984,21 @@ int launch_decode_form(DecodeParams p, cudaStream_t stream) {
   using C = Cfg<T, QH, NW, NS, LPT>;
   // the shared-memory attribute is set once per device and kernel form; the bit mask makes
   // concurrent first calls and processes that alternate devices safe
+  constexpr int smem_bytes = kFused ? C::kSmemFused : C::kSmem;
   static std::atomic<uint64_t> configured{0};
   int dev = 0;
   KPX_CUDA_TRY(cudaGetDevice(&dev));
   auto kern = paged_decode_kernel<T, QH, NW, NS, LPT, kSmall, CPS, kFused>;
   const uint64_t bit = uint64_t(1) << (dev & 63);
   if (dev >= 64 || !(configured.load(std::memory_order_acquire) & bit)) {
-    KPX_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
+    KPX_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     if (dev < 64) configured.fetch_or(bit, std::memory_order_release);
   }
   int grid = device_info().sm_count;
   if (grid > kMaxSms) grid = kMaxSms;
   grid *= CPS;
   p.head_groups = (p.kv_mul + QH - 1) / QH;
-  kern<<<grid, C::kThreads, C::kSmem, stream>>>(p);
+  kern<<<grid, C::kThreads, smem_bytes, stream>>>(p);
   KPX_CUDA_TRY(cudaGetLastError());
   return cuda_status(cudaGetLastError());
 }

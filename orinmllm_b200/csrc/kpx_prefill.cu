@@ -69,6 +69,15 @@ extern "C" int kpx_paged_prefill(void* out, const void* q, const void* k_pool, c
                                  void* stream) {
   if (!layout_ok(layout) || !cu_q_lens_host || !start_pos_host || batch < 0 || !workspace)
     return KPX_ERR_INVALID_ARGUMENT;
+  // everything both device paths dereference or store 16 bytes at a time is checked here, on
+  // the host, so that a bad argument is an error code and never a device fault
+  if (!out || !q || !k_pool || !v_pool || num_q_heads <= 0 || num_q_heads % layout->num_kv_heads)
+    return KPX_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(q) |
+       reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool) |
+       reinterpret_cast<uintptr_t>(workspace)) & 15)
+    return KPX_ERR_INVALID_ARGUMENT;
+  if (block_table && max_blocks_per_seq <= 0) return KPX_ERR_INVALID_ARGUMENT;
   if (batch == 0) return KPX_OK;
   if (cu_q_lens_host[0] != 0) return KPX_ERR_INVALID_ARGUMENT;
   for (int32_t b = 0; b < batch; ++b)
@@ -76,6 +85,14 @@ extern "C" int kpx_paged_prefill(void* out, const void* q, const void* k_pool, c
       return KPX_ERR_INVALID_ARGUMENT;
   const int32_t total_q = cu_q_lens_host[batch];
   if (batch > total_q && total_q > 0) return KPX_ERR_INVALID_ARGUMENT;  // sequences without queries
+  if (block_table) {
+    // the last position a sequence attends to must lie inside its table row
+    for (int32_t b = 0; b < batch; ++b) {
+      const int64_t end = int64_t(start_pos_host[b]) + (cu_q_lens_host[b + 1] - cu_q_lens_host[b]);
+      if ((end + layout->block_size - 1) / layout->block_size > max_blocks_per_seq)
+        return KPX_ERR_INVALID_ARGUMENT;
+    }
+  }
   if (total_q == 0) return KPX_OK;
   const int64_t need = kpx_prefill_workspace_bytes(total_q, num_q_heads, layout->num_kv_heads,
                                                    layout->head_size);

@@ -309,6 +309,71 @@ static void test_paged_layers_fp16() {
   }
 }
 
+// Plain multi-head attention, 32 KV heads (Llama-2-7B style): beyond what the library's
+// built-in scratch serves, so the adapters must fall back to the CudaConfig's workspace; and
+// without a CudaConfig the failure must come back as a Status, not as stale output.
+static void test_mha_32_kv_heads_falls_back_to_the_config_workspace() {
+  std::printf("MultiHeadAttention / FlashAttentionDecodeLayer, 32 Q = 32 KV heads\n");
+  const int H = 32, HKV = 32, D = 128, S = 96, pos = 70;
+  const int dim = H * D, kv_dim = HKV * D;
+  std::mt19937_64 g(21);
+  std::vector<float> kc = randn(size_t(S) * kv_dim, g), vc = randn(size_t(S) * kv_dim, g), q = randn(dim, g);
+  std::vector<float> score(size_t(H) * S), out_ref(dim);
+  orc_mha(pos, H, 0, S, kv_dim, 1, D, out_ref.data(), q.data(), score.data(), kc.data(), vc.data());
+  auto cfg = std::make_shared<kernel::CudaConfig>();
+  cfg->init();
+  tensor::Tensor dq = device_tensor(DataType::kDataTypeFp32, {dim}, q);
+  tensor::Tensor dkc = device_tensor(DataType::kDataTypeFp32, {1, S, kv_dim}, kc), dvc = device_tensor(DataType::kDataTypeFp32, {1, S, kv_dim}, vc);
+  tensor::Tensor dscore(DataType::kDataTypeFp32, H, S, true, cuda_alloc());
+  {
+    tensor::Tensor dout(DataType::kDataTypeFp32, dim, true, cuda_alloc());
+    op::MultiHeadAttention mha(DeviceType::kDeviceCUDA, 0, 1, kv_dim, S, H, D);
+    mha.set_cuda_config(cfg);
+    mha.set_pos(pos);
+    mha.set_input(0, dq); mha.set_input(1, dscore); mha.set_input(2, dkc); mha.set_input(3, dvc);
+    mha.set_output(0, dout);
+    EXPECT(bool(mha.forward()));
+    cudaStreamSynchronize(cfg->stream);
+    EXPECT(cfg->kv_workspace != nullptr);  // the fallback path ran
+    float err = max_abs_diff(to_host<float>(dout), out_ref);
+    std::printf("  with a CudaConfig: max abs err %.3e\n", err);
+    EXPECT(err <= 2e-3f);
+  }
+  {
+    tensor::Tensor dout(DataType::kDataTypeFp32, dim, true, cuda_alloc());
+    op::FlashAttentionDecodeLayer fa(DeviceType::kDeviceCUDA, H, HKV, D, 1, S, kv_dim, false);
+    fa.set_cuda_config(cfg);
+    fa.set_layer_index(0);
+    fa.set_pos(pos);
+    fa.set_input(0, dq); fa.set_input(1, dout); fa.set_input(2, dkc); fa.set_input(3, dvc);
+    EXPECT(bool(fa.forward()));
+    cudaStreamSynchronize(cfg->stream);
+    EXPECT(max_abs_diff(to_host<float>(dout), out_ref) <= 2e-3f);
+  }
+  {
+    // no CudaConfig: nowhere to keep a workspace; the kernel function reports and changes nothing
+    tensor::Tensor dout = device_tensor(DataType::kDataTypeFp32, {dim}, std::vector<float>(dim, -7.f));
+    std::printf("  (one '[kuiper-b200] ... static scratch' line is expected here)\n");
+    kernel::mha_kernel_cu(pos, H, 0, S, kv_dim, 1, D, dout, dq, dscore, dkc, dvc, DeviceType::kDeviceCUDA, nullptr);
+    cudaDeviceSynchronize();
+    std::vector<float> untouched = to_host<float>(dout);
+    EXPECT(untouched[0] == -7.f && untouched[dim - 1] == -7.f);
+  }
+  {
+    // the status a void kernel function met reaches the layer's caller
+    cfg->note_status(KPX_ERR_WORKSPACE_TOO_SMALL);
+    tensor::Tensor dout(DataType::kDataTypeFp32, dim, true, cuda_alloc());
+    op::MultiHeadAttention mha(DeviceType::kDeviceCUDA, 0, 1, kv_dim, S, H, D);
+    mha.set_cuda_config(cfg);
+    mha.set_pos(pos);
+    mha.set_input(0, dq); mha.set_input(1, dscore); mha.set_input(2, dkc); mha.set_input(3, dvc);
+    mha.set_output(0, dout);
+    base::Status st = mha.forward();
+    EXPECT(!st && st.get_err_code() == KPX_ERR_WORKSPACE_TOO_SMALL);
+    EXPECT(bool(mha.forward()));  // taken once, then clean again
+  }
+}
+
 int main() {
   int n = 0;
   if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
@@ -319,6 +384,7 @@ int main() {
   test_flash_decode_fp16();
   test_prefill_chunk_fp32();
   test_paged_layers_fp16();
+  test_mha_32_kv_heads_falls_back_to_the_config_workspace();
   std::printf("%d checks, %d failed\n", g_checks, g_fail);
   return g_fail ? 1 : 0;
 }

@@ -18,7 +18,7 @@ from orinmllm_b200 import capi, kvm, sched
 class ServingSim:
     def __init__(self, num_layers, q_heads, kv_heads, num_blocks, dtype=torch.float16, vocab=4096, seed=0,
                  max_positions=8192, prefill_chunk=512, max_prefill_tokens=2048, max_decode_batch=256,
-                 use_prefix_cache=True, record=False, theta=1e6, poison=False):
+                 use_prefix_cache=True, record=False, theta=1e6, poison=False, record_ids=None):
         self.L, self.H, self.HKV, self.D, self.BS = num_layers, q_heads, kv_heads, 128, 16
         self.nb, self.dtype, self.vocab = num_blocks, dtype, vocab
         self.scale = 1.0 / np.sqrt(self.D)
@@ -51,6 +51,7 @@ class ServingSim:
         self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device="cuda")
         capi.workspace_init(self.ws, self.ws_bytes)
         self.record = record
+        self.record_ids = None if record_ids is None else set(int(r) for r in record_ids)  # None: every request
         self.outputs = {}       # request id -> {position: [L, dim] output rows (host, float32)} when record
         self.kv_bytes_decoded = 0   # algorithmic K/V bytes the decode launches had to read
         self.decode_launches = 0
@@ -87,6 +88,8 @@ class ServingSim:
                 outs.append(out.float().cpu().numpy())
         if self.record:
             for i, rid in enumerate(p.request_ids):
+                if self.record_ids is not None and int(rid) not in self.record_ids:
+                    continue
                 a, b = p.cu_q_lens[i], p.cu_q_lens[i + 1]
                 store = self.outputs.setdefault(int(rid), {})
                 for t in range(a, b):
@@ -121,6 +124,8 @@ class ServingSim:
         self.kv_bytes_decoded += int(d.seq_lens.sum()) * self.HKV * self.D * self.kp.element_size() * 2 * self.L
         if self.record:
             for i, rid in enumerate(d.request_ids):
+                if self.record_ids is not None and int(rid) not in self.record_ids:
+                    continue
                 self.outputs.setdefault(int(rid), {})[int(d.positions[i])] = np.stack([o[i] for o in outs])
 
     @staticmethod
