@@ -52,6 +52,14 @@ def peaks():
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
+def tensor_peak():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        d = json.loads(f.read_text())
+        return float(d["bf16_tflops_sustained"]), "measured (MEASURED_PEAKS.json bf16_tflops_sustained)"
+    return 1400.0, "fallback (1.4 PFLOP/s sustained, earlier measurement on this pool)"
+
+
 def make_lens(seed, batch=BATCH):
     rng = np.random.default_rng(seed)
     return rng.integers(CTX_LO, CTX_HI + 1, size=batch).astype(np.int32)
@@ -296,6 +304,137 @@ class DecodeWorkload:
         return LAYERS * BATCH * Q_HEADS * HEAD * 2
 
 
+# ------------------------------------------------- the path's other kernels, same run
+def _median_ms(torch, fn, reps, flush=None):
+    ms = []
+    for _ in range(reps):
+        if flush is not None:
+            flush.sum()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms.append(e0.elapsed_time(e1))
+    return float(np.median(ms))
+
+
+def extra_prefill(torch, capi):
+    """Chunked prefill at the Qwen2.5-7B attention shape (28 Q / 4 KV heads, d 128, bf16, block 16):
+    4 sequences of 2048-token prompts in 512-token chunks, seeded random block placement.  Device
+    time of the four chunk calls of a layer (each queued several times back to back behind a
+    filler kernel, CUDA events around the queue), FLOPs counted causal-exact."""
+    H, HKV, D, BS, B, PROMPT, CHUNK = 28, 4, HEAD, BLOCK, 4, 2048, 512
+    rng = np.random.default_rng(3)
+    nb = int(B * PROMPT / BS * 1.25)
+    table = rng.permutation(nb).astype(np.int32)[:B * PROMPT // BS].reshape(B, PROMPT // BS).copy()
+    dt = torch.bfloat16
+    kp = torch.randn(nb, HKV, BS, D, device="cuda", dtype=dt)
+    vp = torch.randn(nb, HKV, BS, D, device="cuda", dtype=dt)
+    q = torch.randn(B * CHUNK, H * D, device="cuda", dtype=dt)
+    out = torch.empty_like(q)
+    lay = capi.layout_paged(capi.KPX_BF16, HKV, D, BS, nb)
+    bt = torch.from_numpy(table).cuda()
+    cu = (np.arange(B + 1) * CHUNK).astype(np.int32)
+    nbytes = capi.prefill_workspace_bytes(B * CHUNK, H, HKV, D)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    capi.workspace_init(ws, nbytes)
+    nch = PROMPT // CHUNK
+    flops = [B * 4.0 * H * D * sum(c * CHUNK + i + 1 for i in range(CHUNK)) for c in range(nch)]
+    starts = [np.full(B, c * CHUNK, np.int32) for c in range(nch)]
+    call = lambda c: capi.paged_prefill(out, q, kp, vp, lay, bt, table.shape[1], cu, starts[c], B, H,
+                                        1 / np.sqrt(D), ws, nbytes)
+    for c in range(nch):
+        call(c)
+    torch.cuda.synchronize()
+    filler = torch.empty(1 << 27, dtype=torch.float32, device="cuda")
+    queued, total_ms = 10, 0.0
+    for c in range(nch):
+        for _ in range(3):
+            filler.add_(1.0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(queued):
+            call(c)
+        e1.record()
+        torch.cuda.synchronize()
+        total_ms += e0.elapsed_time(e1) / queued
+    status = capi.workspace_status(ws)
+    peak, src = tensor_peak()
+    tflops = sum(flops) / total_ms / 1e9
+    return {"workload": "chunked prefill, 28 Q / 4 KV heads, bf16, 4 x 2048 tokens in chunks of 512",
+            "kernel": "prefill_tc_kernel", "tflops": round(tflops, 1), "frac_of_sustained": round(tflops / peak, 4),
+            "peak_tflops": peak, "peak_source": src, "us_per_layer": round(total_ms * 1e3, 1),
+            "flops_per_layer": sum(flops), "launches": queued * nch, "status": status}
+
+
+def extra_append(torch, capi):
+    """kpx_append and kpx_rope_append alone on 131 072 tokens at the Qwen3-8B shape (fp16, new rows
+    filling whole blocks at seeded random places in the pool): bytes read + written / device time,
+    L2 flushed before each launch."""
+    n, HKV, H, D, BS = 131072, KV_HEADS, Q_HEADS, HEAD, BLOCK
+    rng = np.random.default_rng(77)
+    nb = int(np.ceil(n / BS * 1.25))
+    kp = torch.zeros(nb, HKV, BS, D, device="cuda", dtype=torch.float16)
+    vp = torch.zeros_like(kp)
+    lay = capi.layout_paged(capi.KPX_F16, HKV, D, BS, nb)
+    max_pos = 4096
+    sin = torch.empty(max_pos * D, device="cuda", dtype=torch.float32)
+    cos = torch.empty_like(sin)
+    capi.sin_cos_cache(sin, cos, D, max_pos, ROPE_THETA)
+    blocks = rng.permutation(nb)[:n // BS].astype(np.int64)
+    slots = torch.from_numpy((blocks[:, None] * BS + np.arange(BS)[None, :]).reshape(-1)).cuda()
+    pos = torch.from_numpy((np.arange(n) % max_pos).astype(np.int32)).cuda()
+    q = torch.randn(n, H * D, device="cuda", dtype=torch.float16)
+    k = torch.randn(n, HKV * D, device="cuda", dtype=torch.float16)
+    v = torch.randn(n, HKV * D, device="cuda", dtype=torch.float16)
+    flush = torch.zeros(64 << 20, dtype=torch.int32, device="cuda")
+    peak, src = peaks()
+    t_plain = _median_ms(torch, lambda: capi.append(kp, vp, lay, k, v, slot_mapping=slots, num_tokens=n), 7, flush)
+    b_plain = n * HKV * D * 2 * 2 * 2
+    t_rope = _median_ms(torch, lambda: capi.rope_append(q, k, v, H, pos, sin, cos, kp, vp, lay, slots, n), 7, flush)
+    b_rope = n * D * 2 * ((H + 2 * HKV) + (H + HKV) + 2 * HKV)
+    return {"workload": "131072 tokens, 8 KV heads x 128, fp16, block 16, random block placement",
+            "kernel": "append_token_kernel", "gbs": round(b_plain / t_plain / 1e6, 1),
+            "frac": round(b_plain / t_plain / 1e6 / peak, 4), "us": round(t_plain * 1e3, 1), "bytes": b_plain,
+            "rope_append": {"kernel": "rope_append_kernel", "gbs": round(b_rope / t_rope / 1e6, 1),
+                            "frac": round(b_rope / t_rope / 1e6 / peak, 4), "us": round(t_rope * 1e3, 1),
+                            "bytes": b_rope},
+            "peak": peak, "peak_source": src}
+
+
+def extra_prefix_reuse(torch, capi):
+    """256 requests sharing a 1024-token prefix + 256 own tokens, 128 decode steps each, through
+    the request scheduler on 2 layers (Qwen3-8B attention shape, fp16, block 16): pool usage with
+    and without sharing, copy-on-write events, and the decode kernel's algorithmic KV GB/s on the
+    full-batch steps (CUDA events around each decode launch; the median launch)."""
+    from tests.serving_sim import ServingSim
+    prefix, suffix, n_req, gen, layers = 1024, 256, 256, 129, 2
+    sim = ServingSim(layers, Q_HEADS, KV_HEADS, num_blocks=8192, seed=7, max_positions=2048, prefill_chunk=512,
+                     max_prefill_tokens=4096, max_decode_batch=256)
+    rng = np.random.default_rng(4)
+    common = rng.integers(0, 151936, prefix)
+    sim.sched.submit(np.concatenate([common, rng.integers(0, 151936, suffix)]), 1, also_register=prefix)
+    sim.run()
+    for _ in range(n_req - 1):
+        sim.sched.submit(np.concatenate([common, rng.integers(0, 151936, suffix)]), gen)
+    sim.decode_events = []
+    sim.run()
+    st = sim.sched.stats()
+    ev = [(e0.elapsed_time(e1), b) for e0, e1, b in sim.decode_events]
+    top = max(b for _, b in ev)
+    ev = [(m, b) for m, b in ev if b >= 0.9 * top]
+    peak, _ = peaks()
+    gbs = float(np.median([b / m for m, b in ev])) / 1e6
+    return {"workload": "256 requests = 1024 shared + 256 own tokens, 128 decode steps, 2 layers, bs 255",
+            "blocks_in_use": int(st["peak_blocks_in_use"]),
+            "blocks_unshared": n_req * ((prefix + suffix + gen - 1 + BLOCK - 1) // BLOCK),
+            "reused_tokens": int(st["reused_tokens"]), "cow_events": int(sim.manager.cow_events),
+            "decode_gbs": round(gbs, 1), "decode_frac": round(gbs / peak, 4),
+            "decode_launch_us": round(float(np.median([m for m, _ in ev])) * 1e3, 1),
+            "decode_launches_timed": len(ev), "kv_bytes_per_launch": int(np.mean([b for _, b in ev]))}
+
+
 # ------------------------------------------------------------------ CPU legs (oracle)
 def cpu_decode_sample(threads, reps, seed=SEED):
     """Times the CPU restatement of the reference's fp32 MHA path (the oracle: test
@@ -327,17 +466,62 @@ def cpu_decode_sample(threads, reps, seed=SEED):
     return nbytes / 1e9 / float(np.mean(times)), float(np.mean(times)), nbytes
 
 
+def cpu_reference_sample(threads, reps, seed=SEED):
+    """Times the REFERENCE's own CPU MHA (kernel::mha_kernel and the matmul / softmax / scale-sum
+    kernels it calls, compiled unmodified into oracle/_ref/libref_cpu.so) on one layer of the
+    workload.  The reference serves one sequence at a time from a contiguous fp32 cache, so every
+    sequence's K/V is laid out that way beforehand (untimed) and the 64 single-sequence calls are
+    spread over `threads` host threads.  Returns None where the library has not been built."""
+    from concurrent.futures import ThreadPoolExecutor
+    from tests import refcpu
+    ref = refcpu.load(sequential=False)
+    if ref is None:
+        return None
+    lens = make_lens(seed) + 1
+    rng = np.random.default_rng(seed + 7)
+    kv_dim = KV_HEADS * HEAD
+    caches = [(rng.standard_normal((1, int(n), kv_dim), np.float32), rng.standard_normal((1, int(n), kv_dim), np.float32))
+              for n in lens]
+    q = rng.standard_normal((BATCH, Q_HEADS * HEAD), np.float32)
+
+    def one(b):
+        n = int(lens[b])
+        return ref.mha(n - 1, Q_HEADS, 0, n, kv_dim, Q_HEADS // KV_HEADS, HEAD, 1, q[b], caches[b][0], caches[b][1])
+
+    one(int(np.argmin(lens)))  # first call creates the reference's allocator singleton
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        if threads == 1:
+            for b in range(BATCH):
+                one(b)
+        else:
+            with ThreadPoolExecutor(max_workers=threads) as pool:
+                list(pool.map(one, range(BATCH)))
+        times.append(time.perf_counter() - t0)
+    nbytes = kv_bytes_per_layer(lens)
+    return nbytes / 1e9 / float(np.mean(times)), float(np.mean(times)), nbytes
+
+
 def run_reference(args):
-    """Reference arm: the reference's own CPU path for this hot path cannot be compiled here
-    (it needs Armadillo + glog), so the timed code is its restatement under oracle/, on all
-    host threads.  One step = one layer of the workload (a bounded sample of the 36)."""
+    """Reference arm: the reference's own CPU implementation of the path on the host cores.  Where
+    oracle/_ref/libref_cpu.so exists (the reference's cpu/*.cpp compiled unmodified against the
+    glog / Armadillo stand-ins) that is what is timed, else its plain-C restatement under
+    oracle/.  One step = one layer of the workload (a bounded sample of the 36), all host
+    threads."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     # all host cores this process may run on (torchrun presets OMP_NUM_THREADS=1, so the OpenMP
     # default would be a single thread)
     threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
-    gbs, sec, nbytes = cpu_decode_sample(threads, max(1, args.steps))
+    got = cpu_reference_sample(threads, max(1, args.steps))
+    kind = "reference"
+    if got is None:
+        got, kind = cpu_decode_sample(threads, max(1, args.steps)), "port"
+    gbs, sec, nbytes = got
+    what = ("kernel::mha_kernel of the reference (compiled from its sources), one call per sequence over a "
+            "contiguous fp32 cache") if kind == "reference" else "fp32 oracle (plain-C restatement)"
     line = {
         "impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -345,8 +529,8 @@ def run_reference(args):
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "paged GQA decode, Qwen3-8B attention shape, bs=64, ctx U[128,4096], block 16",
                    "sample": "1 of 36 layers per step, all 64 sequences"},
-        "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
-                         "sample": "one layer (all 64 sequences, %d KV bytes) per step, fp32 oracle" % nbytes},
+        "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": kind,
+                         "sample": "one layer (all 64 sequences, %d KV bytes) per step; %s" % (nbytes, what)},
         "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "tokens_per_s": round(BATCH / (sec * LAYERS), 3),
     }
@@ -459,9 +643,25 @@ def run_gpu(args):
     value = tot[0] / 1e9 / (ms_resident / 1e3)
     e2e = tot[1] / 1e9 / (ms_e2e / 1e3)
     per_launch_bytes = bytes_resident / (K * LAYERS)
-    avg_decode_ms = float(np.mean(decode_ms))
-    achieved = per_launch_bytes / 1e9 / (avg_decode_ms / 1e3)
-    cpu_gbs, cpu_sec, cpu_bytes = cpu_decode_sample(1, 3)
+    # Per-launch duration inside the timed region: the region holds K x 36 decode launches (and
+    # their small RoPE+append launches) and nothing else, so region time / launches is the
+    # average a decode launch takes there.  Launches of neighbouring layers overlap, which
+    # is why this is shorter than one launch timed alone (reported beside it).
+    in_region_ms = ms_resident / (K * LAYERS)
+    achieved = per_launch_bytes / 1e9 / (in_region_ms / 1e3)
+    isolated_ms = float(np.mean(decode_ms))
+    isolated = per_launch_bytes / 1e9 / (isolated_ms / 1e3)
+    got = cpu_reference_sample(1, 1)
+    cpu_kind = "reference"
+    if got is None:
+        got, cpu_kind = cpu_decode_sample(1, 3), "port"
+    cpu_gbs, cpu_sec, cpu_bytes = got
+    chains = wl.chains if use_graph else 1
+    kernels = wl.per_layer * LAYERS
+    launch = ("one CUDA graph replay per step: %d kernels, layer l on chain l %% %d (layers are independent: own pool, "
+              "own rows, own workspace per chain), so a layer's CTAs take the SMs the previous layer's CTAs leave; "
+              "end to end: plus 108 H2D and 36 D2H copies on side streams" % (kernels, chains)) if use_graph \
+        else "one launch per kernel, one stream"
     line = {
         "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": round(ms_resident / K, 4), "higher_is_better": True,
@@ -471,8 +671,7 @@ def run_gpu(args):
                                "seeded random block table; step = RoPE+append+attend over 36 layers",
                    "layers": LAYERS, "batch_per_gpu": BATCH, "partition": "by request, no collective",
                    "l2": "inputs larger than L2: every layer has its own 0.66 GB pool",
-                   "launch": ("one CUDA graph replay per step (72 kernels; end to end: plus 108 H2D and 36 D2H "
-                              "copies on side streams)") if use_graph else "one launch per kernel"},
+                   "launch": launch, "kernels_per_layer": wl.per_layer, "chains": chains},
         "tokens_per_s": round(world * BATCH / (ms_resident / K / 1e3), 1),
         "pct_of_8TBs_per_gpu": round(100 * value / world / 8000.0, 2),
         "e2e": {"value": round(e2e, 1), "unit": "GB/s", "h2d_bytes_per_step": wl.h2d_bytes_per_step(),
@@ -481,16 +680,33 @@ def run_gpu(args):
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "kernel": "paged_decode_kernel", "achieved": round(achieved, 1),
                      "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "avg_launch_us": round(avg_decode_ms * 1e3, 2),
-                     "timed": ("CUDA events around each decode launch of K steps launched one by one right after "
-                               "the timed graph replays") if use_graph else "CUDA events inside the timed region",
+                     "frac": round(achieved / peak, 4), "avg_launch_us": round(in_region_ms * 1e3, 2),
+                     "timed": "CUDA events around the timed region / decode launches inside it (launches of "
+                              "neighbouring layers overlap; the layer's RoPE+append launch is inside too)",
+                     "isolated": {"launch_us": round(isolated_ms * 1e3, 2), "achieved": round(isolated, 1),
+                                  "frac": round(isolated / peak, 4),
+                                  "timed": ("CUDA events around each decode launch of K steps launched one by one, "
+                                            "nothing else on the GPU, right after the timed region; launch latency "
+                                            "included")},
                      "algorithmic_bytes_per_launch": int(per_launch_bytes),
                      "traffic": int(per_launch_bytes * TRAFFIC_RATIO), "traffic_note": TRAFFIC_NOTE},
-        "cpu_baseline": {"value": round(cpu_gbs, 3), "unit": "GB/s", "cores": 1, "kind": "port",
-                         "sample": "one layer of the workload (64 sequences, %d KV bytes), fp32 oracle, "
-                                   "mean of 3 runs, %.2f s each" % (cpu_bytes, cpu_sec)},
+        "cpu_baseline": {"value": round(cpu_gbs, 3), "unit": "GB/s", "cores": 1, "kind": cpu_kind,
+                         "sample": "one layer of the workload (64 sequences, %d KV bytes), %s, %.2f s" % (
+                             cpu_bytes, "the reference's own kernel::mha_kernel compiled from its sources, one "
+                             "call per sequence" if cpu_kind == "reference" else "fp32 oracle, mean of 3 runs", cpu_sec)},
         "clocks": clocks,
     }
+    if world == 1 and not args.no_extras:
+        # the path's other kernels, measured in this same run after the headline
+        del wl
+        torch.cuda.empty_cache()
+        from orinmllm_b200 import capi
+        for key, fn in (("prefill", extra_prefill), ("append", extra_append), ("prefix_reuse", extra_prefix_reuse)):
+            try:
+                line[key] = fn(torch, capi)
+            except Exception as exc:  # the headline stands on its own
+                line[key] = {"error": repr(exc)[:200]}
+            torch.cuda.empty_cache()
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -512,7 +728,9 @@ def main():
                     help="parallel chains the graph's independent layers are captured on")
     ap.add_argument("--fused", action="store_true",
                     help="one launch per layer (kpx_rope_append_decode) instead of kpx_rope_append + kpx_paged_decode")
-    ap.add_argument("--variant", type=int, default=0)
+    ap.add_argument("--variant", type=int, default=0, help="decode tuning variant (experiments)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the prefill / append / prefix-reuse measurements after the headline")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel separately instead of replaying CUDA graphs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup

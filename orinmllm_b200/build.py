@@ -114,9 +114,48 @@ def build_host(force=False, verbose=False) -> Path | None:
     return so
 
 
+def _nccl_dirs():
+    """(include dir, library file) of the NCCL this process would load: the one packaged with the
+    Python environment if there is one (torch loads that), else the system's."""
+    try:
+        import importlib.util
+        spec = importlib.util.find_spec("nvidia.nccl")
+        if spec and spec.submodule_search_locations:
+            base = Path(list(spec.submodule_search_locations)[0])
+            lib = base / "lib" / "libnccl.so.2"
+            if (base / "include" / "nccl.h").exists() and lib.exists():
+                return base / "include", lib
+    except Exception:
+        pass
+    for inc, lib in ((Path("/usr/include"), Path("/usr/lib/x86_64-linux-gnu/libnccl.so.2")),):
+        if (inc / "nccl.h").exists() and lib.exists():
+            return inc, lib
+    return None
+
+
+def build_comm(force=False, verbose=False) -> Path | None:
+    """csrc/comm/*.cpp (the NCCL all-gather of the KV-head-sharded mode) -> lib/libkpx_comm.so.
+    Skipped (None) where no NCCL is installed: only the multi-GPU sharded mode needs it."""
+    srcs = sorted((CSRC / "comm").glob("*.cpp"))
+    found = _nccl_dirs()
+    if not srcs or found is None:
+        return None
+    inc, lib = found
+    so = LIB / "libkpx_comm.so"
+    if force or _newer(so, srcs + _headers()):
+        nvcc = _nvcc()
+        cuda_root = Path(nvcc).resolve().parent.parent
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-fvisibility=hidden",
+               "-I", INCLUDE, "-I", inc, "-I", cuda_root / "include", "-o", so, *srcs,
+               str(lib), f"-Wl,-rpath,{lib.parent}", f"-L{cuda_root / 'lib64'}", "-lcudart"]
+        _run(cmd, verbose)
+    return so
+
+
 def build_all(force=False, verbose=False, ptxas_info=False):
     build_kpx(force, verbose, ptxas_info)
     build_host(force, verbose)
+    build_comm(force, verbose)
 
 
 if __name__ == "__main__":

@@ -77,3 +77,51 @@ def test_request_dealing_and_prefix_routing():
         multigpu.kv_head_shard(0, 3, 32, 8)
     kv, qh = multigpu.kv_head_shard(3, 4, 32, 8)
     assert (kv.start, kv.stop, qh.start, qh.stop) == (6, 8, 24, 32)
+
+
+def test_dealing_by_load_balances_skewed_lengths():
+    rng = np.random.default_rng(3)
+    # a skewed set: a few very long requests among many short ones
+    lens = np.concatenate([rng.integers(128, 600, 480), rng.integers(20000, 32768, 32)])
+    rng.shuffle(lens)
+    for world in (2, 4, 8):
+        for equal in (False, True):
+            deal = multigpu.deal_requests_by_load(lens, world, equal_counts=equal)
+            assert sorted(i for ids in deal for i in ids) == list(range(len(lens)))
+            loads = [int(lens[ids].sum()) for ids in deal]
+            assert (max(loads) - min(loads)) / np.mean(loads) < 0.02, (world, equal, loads)
+            if equal:
+                assert {len(ids) for ids in deal} == {len(lens) // world}
+        # contiguous dealing of the same set is far off balance
+        naive = [int(lens[multigpu.deal_requests(len(lens), world, r)].sum()) for r in range(world)]
+        assert (max(naive) - min(naive)) / np.mean(naive) > 0.05
+    assert multigpu.deal_requests_by_load([5.0, 1.0, 1.0], 2) == [[0], [1, 2]]
+
+
+def _deal_worker(rank, world, port, result):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    # every rank draws the same global set and computes the same deal; the totals add up
+    lens = np.random.default_rng(2024).integers(128, 4097, size=64 * world)
+    mine = multigpu.deal_requests_by_load(lens, world, equal_counts=True)[rank]
+    tot = multigpu.sum_over_ranks([float(len(mine)), float(lens[mine].sum())], world)
+    if rank == 0:
+        result.put((tot, float(lens.sum()), float(lens[mine].sum())))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_gloo_dealing_by_load_is_consistent():
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_deal_worker, args=(r, 2, port, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    tot, all_tokens, rank0_tokens = result.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert tot == [128.0, all_tokens]
+    assert abs(rank0_tokens - all_tokens / 2) / all_tokens < 0.005
