@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Headline benchmark: paged GQA decode attention at the Qwen3-8B attention shape.
 
-Workload (BASELINE.json configs[1]): 32 Q heads, 8 KV heads, head_dim 128, fp16 KV, block
+Workload: 32 Q heads, 8 KV heads, head_dim 128, fp16 KV, block
 size 16, batch 64, per-sequence context lengths uniform in [128, 4096] from a seed, block
 pool = total blocks x 1.25 with a seeded random block table, Q/K/V ~ N(0,1).  One step =
 one decode step of the KV-cache hot path over all 36 layers: per layer, RoPE the new Q/K
@@ -106,15 +106,19 @@ class ClockSampler(threading.Thread):
 class DecodeWorkload:
     """Per-GPU state of the headline workload, resident in HBM."""
 
-    def __init__(self, rank, total_steps, device, chains=1, fused=True):
+    def __init__(self, rank, total_steps, device, chains=1, fused=True, world=1):
         import torch
         self.chains, self.fused = chains, fused
         self.per_layer = 1 if fused else 2
         from orinmllm_b200 import capi
         self.torch, self.capi, self.dev = torch, capi, device
-        # weak scaling: every GPU gets the same amount of work (the same context lengths); block
-        # placement and data differ per rank
-        self.lens0 = make_lens(SEED)
+        # weak scaling: one global draw of 64 x N requests, dealt to the ranks by KV bytes (longest
+        # first to the least loaded rank, 64 requests each): every GPU gets the same batch size and
+        # nearly the same bytes, but its own lengths.  N = 1 is the plain 64-request draw.
+        from orinmllm_b200 import multigpu
+        all_lens = make_lens(SEED, BATCH * world)
+        mine = multigpu.deal_requests_by_load(all_lens, world, equal_counts=True)[rank]
+        self.lens0 = np.ascontiguousarray(all_lens[mine])
         rng = np.random.default_rng(SEED + 1000 * rank + 1)
         final = self.lens0 + total_steps
         nblk = (final + BLOCK - 1) // BLOCK
@@ -558,9 +562,11 @@ def run_gpu(args):
     use_graph = not args.no_graph
     total_steps = 2 * (W + K) + K + 2
     wl = DecodeWorkload(rank, total_steps, device, chains=max(1, args.chains) if use_graph else 1,
-                        fused=args.fused)
+                        fused=args.fused, world=world)
     if args.variant:
         wl.capi.lib().kpx_internal_set_decode_variant(args.variant)
+    if args.waves:
+        wl.capi.lib().kpx_internal_set_decode_waves(args.waves)
 
     def barrier():
         if world > 1:
@@ -669,7 +675,9 @@ def run_gpu(args):
         "config": {"workload": "paged GQA decode, Qwen3-8B attention shape (32 Q / 8 KV heads, d=128), "
                                "fp16 KV, block 16, bs=64 per GPU, ctx U[128,4096], pool x1.25, "
                                "seeded random block table; step = RoPE+append+attend over 36 layers",
-                   "layers": LAYERS, "batch_per_gpu": BATCH, "partition": "by request, no collective",
+                   "layers": LAYERS, "batch_per_gpu": BATCH,
+                   "partition": "by request, no collective: one global draw of 64 x N requests dealt to the ranks "
+                                "by KV bytes, 64 each",
                    "l2": "inputs larger than L2: every layer has its own 0.66 GB pool",
                    "launch": launch, "kernels_per_layer": wl.per_layer, "chains": chains},
         "tokens_per_s": round(world * BATCH / (ms_resident / K / 1e3), 1),
@@ -729,6 +737,7 @@ def main():
     ap.add_argument("--fused", action="store_true",
                     help="one launch per layer (kpx_rope_append_decode) instead of kpx_rope_append + kpx_paged_decode")
     ap.add_argument("--variant", type=int, default=0, help="decode tuning variant (experiments)")
+    ap.add_argument("--waves", type=int, default=0, help="waves of CTAs per overlapped decode launch (experiments)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the prefill / append / prefix-reuse measurements after the headline")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel separately instead of replaying CUDA graphs")

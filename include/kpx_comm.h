@@ -30,6 +30,8 @@ typedef struct kpx_comm kpx_comm;
  * 7 = invalid argument). */
 KPX_COMM_API int kpx_comm_make_id(void* id_out);
 KPX_COMM_API int kpx_comm_create(kpx_comm** out, const void* id, int32_t world, int32_t rank);
+/* Destroy every CUDA graph that captured an exchange of this communicator first: NCCL keeps the
+ * communicator alive for captured work, and the call would wait for ever. */
 KPX_COMM_API int kpx_comm_destroy(kpx_comm* comm);
 KPX_COMM_API int kpx_comm_world(const kpx_comm* comm);
 KPX_COMM_API int kpx_comm_rank(const kpx_comm* comm);

@@ -70,6 +70,7 @@ inline void decode_contiguous(const int32_t* pos_dev, int32_t host_len, int32_t 
                               const tensor::Tensor& query, const tensor::Tensor& key_cache,
                               const tensor::Tensor& value_cache, CudaConfig* config, const char* what) {
   kpx_kv_layout lay = contiguous_layout(kpx_dtype(key_cache), kv_dim, head_size);
+  lay.num_blocks = (seq_len + lay.block_size - 1) / lay.block_size;  // rows the layer's cache holds
   report(decode_any(const_cast<uint8_t*>(out.ptr<uint8_t>()), query.ptr<uint8_t>(),
                     layer_base(key_cache, layer_index, seq_len, kv_dim),
                     layer_base(value_cache, layer_index, seq_len, kv_dim), &lay, nullptr, 0, pos_dev,

@@ -13,6 +13,7 @@ int g_decode_variant = 0;
 // g_min_blocks_per_range blocks while at least g_min_warps_per_sm warps per SM stay active.
 int g_small_below = 12, g_min_blocks_per_range = 12, g_min_warps_per_sm = 4;
 // Test-only: polls before a bounded wait gives up, and the warp whose first tile never comes.
+int g_decode_waves = 0;
 uint32_t g_wait_limit = kWaitLimit;
 int g_withhold_worker = -1;
 }  // namespace decode
@@ -23,6 +24,9 @@ using namespace kpx::decode;
 
 extern "C" __attribute__((visibility("default"))) void kpx_internal_set_decode_variant(int v) {
   g_decode_variant = v;
+}
+extern "C" __attribute__((visibility("default"))) void kpx_internal_set_decode_waves(int waves) {
+  g_decode_waves = waves;
 }
 extern "C" __attribute__((visibility("default"))) void kpx_internal_set_decode_small(int below, int min_blocks,
                                                                                        int min_warps) {
@@ -39,15 +43,23 @@ extern "C" __attribute__((visibility("default"))) void kpx_internal_set_decode_f
   g_withhold_worker = withhold_worker;
 }
 
+namespace {
+constexpr int64_t kSlotBytes = (4 * kD + 8) * sizeof(float);
+// what one wave needs: the least a workspace may hold (the built-in scratch is this size)
+int64_t min_workspace_bytes(int32_t num_q_heads, int32_t num_kv_heads) {
+  return int64_t(kStatusBytes) + counter_bytes(num_q_heads, num_kv_heads) + int64_t(kMinPartialSlots) * kSlotBytes;
+}
+}  // namespace
+
 extern "C" int64_t kpx_decode_workspace_bytes(int32_t batch, int32_t num_q_heads,
                                               int32_t num_kv_heads, int32_t head_size) {
   (void)batch;
   if (num_q_heads <= 0 || num_kv_heads <= 0 || head_size != kD || num_q_heads % num_kv_heads)
     return -1;
-  // header + one counter per item of a launch + 2 partial slots per persistent warp,
-  // each up to 4 heads x (128 + 2) floats
-  return int64_t(kStatusBytes) + counter_bytes(num_q_heads, num_kv_heads) +
-         int64_t(2) * kMaxSms * kMaxWarpsPerCta * (4 * kD + 8) * sizeof(float);
+  // header + one counter per item of a launch + 2 partial slots per range of the line (a
+  // warp's, times the waves a launch may use), each up to 4 heads x (128 + 2) floats
+  return min_workspace_bytes(num_q_heads, num_kv_heads) +
+         int64_t(kMaxWaves - 1) * kMinPartialSlots * kSlotBytes;
 }
 
 extern "C" int kpx_paged_decode(void* out, const void* q, const void* k_pool, const void* v_pool,
@@ -107,9 +119,9 @@ int kpx::decode_rows(void* out, const void* q, const void* k_pool, const void* v
   if ((reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool) |
        reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 15)
     return KPX_ERR_INVALID_ARGUMENT;
-  if (workspace_bytes <
-      kpx_decode_workspace_bytes(batch, num_q_heads, layout->num_kv_heads, layout->head_size))
-    return KPX_ERR_WORKSPACE_TOO_SMALL;
+  if (kpx_decode_workspace_bytes(batch, num_q_heads, layout->num_kv_heads, layout->head_size) < 0)
+    return KPX_ERR_UNIMPLEMENTED;
+  if (workspace_bytes < min_workspace_bytes(num_q_heads, layout->num_kv_heads)) return KPX_ERR_WORKSPACE_TOO_SMALL;
   if (batch == 0) return KPX_OK;
   if (!device_info().ok) return KPX_ERR_CUDA;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -142,7 +154,12 @@ int kpx::decode_rows(void* out, const void* q, const void* k_pool, const void* v
   p.num_kv_heads = layout->num_kv_heads;
   p.kv_mul = num_q_heads / layout->num_kv_heads;
   p.head_groups = 1;
-  p.partial_slots = 2 * kMaxSms * kMaxWarpsPerCta;
+  {
+    // slots the workspace really holds (a workspace of the documented size has room for kMaxWaves)
+    const int64_t room = (workspace_bytes - kStatusBytes - counter_bytes(num_q_heads, layout->num_kv_heads)) / kSlotBytes;
+    const int64_t cap = int64_t(kMinPartialSlots) * kMaxWaves;
+    p.partial_slots = int32_t(room < cap ? room : cap);
+  }
   p.tile_contig = tile_contiguous(layout) ? 1 : 0;
   p.min_blocks_per_range = g_min_blocks_per_range;
   p.min_warps_per_sm = g_min_warps_per_sm;
@@ -186,10 +203,10 @@ int kpx::decode_rows(void* out, const void* q, const void* k_pool, const void* v
 namespace kpx {
 namespace {
 constexpr int kStaticMaxItemsPerSeq = 16;  // num_kv_heads * head groups, e.g. 8 KV heads x 8 query heads each
-constexpr int64_t kStaticCounterBytes = int64_t(kMaxBatch) * kStaticMaxItemsPerSeq * 4;
+constexpr int64_t kStaticCounterBytes = 65536;  // >= kMaxBatch * kStaticMaxItemsPerSeq counters
+static_assert(int64_t(kMaxBatch) * kStaticMaxItemsPerSeq * 4 <= kStaticCounterBytes, "counter area");
 constexpr int64_t kStaticScratchBytes =
-    kStatusBytes + kStaticCounterBytes +
-    int64_t(2) * kMaxSms * kMaxWarpsPerCta * (4 * kD + 8) * sizeof(float);  // 10 715 392 bytes
+    kStatusBytes + kStaticCounterBytes + int64_t(kMinPartialSlots) * kSlotBytes;  // 10 715 392 bytes: one wave
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 }  // namespace
 }  // namespace kpx
@@ -205,10 +222,10 @@ extern "C" int kpx_paged_decode_static(void* out, const void* q, const void* k_p
   const int qh = heads_per_warp(kv_mul);
   const int per_seq = layout->num_kv_heads * ((kv_mul + qh - 1) / qh);
   if (per_seq > kStaticMaxItemsPerSeq) return KPX_ERR_STATIC_SCRATCH_LIMIT;
-  const int64_t need =
-      kpx_decode_workspace_bytes(batch, num_q_heads, layout->num_kv_heads, layout->head_size);
-  if (need < 0) return KPX_ERR_UNIMPLEMENTED;
-  if (need > kStaticScratchBytes) return KPX_ERR_STATIC_SCRATCH_LIMIT;
+  if (kpx_decode_workspace_bytes(batch, num_q_heads, layout->num_kv_heads, layout->head_size) < 0)
+    return KPX_ERR_UNIMPLEMENTED;
+  if (min_workspace_bytes(num_q_heads, layout->num_kv_heads) > kStaticScratchBytes)
+    return KPX_ERR_STATIC_SCRATCH_LIMIT;
   if (!device_info().ok) return KPX_ERR_CUDA;
   // In host code `g_static_scratch` names a host-side stand-in, not device memory: the
   // address a kernel may use comes from cudaGetSymbolAddress, asked once per device with
@@ -240,7 +257,7 @@ extern "C" int kpx_paged_decode_static(void* out, const void* q, const void* k_p
     const int qh = heads_per_warp(num_q_heads / layout->num_kv_heads);
     const size_t slot_bytes = size_t(qh * kD + 8) * sizeof(float);
     uint8_t* partials = static_cast<uint8_t*>(scratch) + kStatusBytes + counter_bytes(num_q_heads, layout->num_kv_heads);
-    KPX_CUDA_TRY(cudaMemsetAsync(partials + size_t(2 * kMaxSms * kMaxWarpsPerCta - 1) * slot_bytes, 0, slot_bytes, s));
+    KPX_CUDA_TRY(cudaMemsetAsync(partials + size_t(kMinPartialSlots - 1) * slot_bytes, 0, slot_bytes, s));
   }
   return kpx_paged_decode(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq,
                           seq_lens, len_bias, batch, num_q_heads, scale, scratch,

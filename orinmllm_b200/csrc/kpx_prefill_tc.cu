@@ -1,15 +1,17 @@
 // Chunked-prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM), 16-bit caches.
 //
 // One CTA = two items (128 query rows x one query head each) of one sequence that share a KV
-// head, so one stream of K/V tiles serves both.  Roles:
-//   warp 9       TMA: Q boxes, then per 128-key tile the (block, head) boxes of K and V through
+// head, so one stream of K/V tiles serves both.  576 threads in roles:
+//   warp 17      TMA: Q boxes, then per 128-key tile the (block, head) boxes of K and V through
 //                the block table into 128-byte-swizzled shared memory (two stages each)
-//   warp 8       one thread issues tcgen05.mma:  S_x = Q_x K^T  into tensor memory (128 columns
-//                per item) and  O_x += P_x V  (A = P read from tensor memory, B = V MN-major
-//                as it sits in the pool); completion is committed to mbarriers
-//   warps 0..7   softmax: S_x -> P_x = exp2(S*c - m) written over S_x as two 16-bit terms
-//                (tcgen05.ld / st; two threads per query row), causal mask on the diagonal,
-//                running maximum moved lazily, O_x rescaled in tensor memory when it moves
+//   warp 16      walks the MMA schedule in step, one elected lane issues tcgen05.mma:
+//                S_x = Q_x K^T  into tensor memory (128 columns per item) and  O_x += P_x V
+//                (A = P read from tensor memory, B = V MN-major as it sits in the pool);
+//                completion is committed to mbarriers
+//   warps 0..7   softmax of item 0, warps 8..15 softmax of item 1: S_x -> P_x = exp2(S*c - m)
+//                written over S_x as two 16-bit terms (tcgen05.ld / st; two threads per query
+//                row), causal mask on the diagonal, running maximum moved lazily, O_x rescaled
+//                in tensor memory when it moves
 // The MMA order  PV_0(j) QK_0(j+1) | PV_1(j) QK_1(j+1)  keeps the tensor core on one item while
 // the softmax threads work on the other.
 // A CTA may own only a range of its pair's key tiles (a call with too few pairs to fill the SMs
@@ -20,6 +22,7 @@
 #include <cuda.h>  // CUtensorMap and the enums of cuTensorMapEncodeTiled (types only; no libcuda link)
 
 #include <algorithm>
+#include <atomic>
 #include <vector>
 
 #include "kpx_common.cuh"
@@ -914,18 +917,20 @@ int prefill_tc(void* out, const void* q, const void* k_pool, const void* v_pool,
   p.kv_mul = kv_mul;
   p.qscale = scale * kLog2e;
   const unsigned grid = unsigned(pairs.size());
-  auto launch = [&](auto kernel, uint64_t* done_mask) -> int {
-    // the shared-memory attribute is per device: set once per device (bit mask of devices 0..63)
+  auto launch = [&](auto kernel, std::atomic<uint64_t>* done_mask) -> int {
+    // the shared-memory attribute is per device: set once per device (atomic bit mask of devices
+    // 0..63, so that concurrent first calls and processes that alternate devices are safe)
     int dev = 0;
     KPX_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev >= 64 || !((*done_mask >> dev) & 1)) {
+    const uint64_t bit = uint64_t(1) << (dev & 63);
+    if (dev >= 64 || !(done_mask->load(std::memory_order_acquire) & bit)) {
       KPX_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-      if (dev < 64) *done_mask |= uint64_t(1) << dev;
+      if (dev < 64) done_mask->fetch_or(bit, std::memory_order_release);
     }
     kernel<<<grid, kThreads, kSmemBytes, stream>>>(p, map_q, map_k, map_v);
     return cuda_status(cudaGetLastError());
   };
-  static uint64_t done_f16 = 0, done_bf16 = 0;  // racing first calls at worst set the attribute twice
+  static std::atomic<uint64_t> done_f16{0}, done_bf16{0};
   const int rc = layout->dtype == KPX_F16 ? launch(prefill_tc_kernel<__half>, &done_f16)
                                           : launch(prefill_tc_kernel<__nv_bfloat16>, &done_bf16);
   if (rc != KPX_OK || merges.empty()) return rc;

@@ -82,7 +82,7 @@ static std::vector<float> randn(size_t n, std::mt19937_64& g) {
   return v;
 }
 
-// BASELINE.json configs[0]: Qwen2.5-1.5B attention shape, 512 cached + 1 new token, fp32, RoPE
+// The CPU-runnable anchor case: Qwen2.5-1.5B attention shape, 512 cached + 1 new token, fp32, RoPE
 // theta 1e6 on the new Q/K, contiguous cache, through RoPELayer -> KVCacheLayer -> MHA.
 static void test_config1_fp32_layers() {
   std::printf("config 1 through RoPEGpuPosLayer / KVCacheLayer / MultiHeadAttention (fp32)\n");

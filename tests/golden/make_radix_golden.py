@@ -96,7 +96,7 @@ def script_cache(seed, n_req, vocab, capacity):
 
 
 def script_config4():
-    """BASELINE.json configs[3] token pattern at reduced count: common 1024-id prefix + unique
+    """The shared-prefix token pattern at reduced count: common 1024-id prefix + unique
     256-id suffixes, ids uniform over [0,151936); the prefix itself is inserted so later
     requests hit it (a prefix shared only inside longer sequences is a miss)."""
     rnd = random.Random(4)

@@ -1,4 +1,4 @@
-"""BASELINE.json configs[2] (chunked prefill at the Qwen2.5-7B attention shape: 28 Q / 4 KV heads,
+"""Chunked prefill at the Qwen2.5-7B attention shape (28 Q / 4 KV heads,
 d=128, bf16, 4 sequences of 2048 tokens in 512-token chunks, block 16, seeded random block
 placement) on random data: times every chunk call with CUDA events (alone and synchronised, then
 queued back to back for the device time) and prints TFLOP/s on the causal-exact FLOP count.  Also the small case the ncu capture under profiles/ was taken on.

@@ -1,4 +1,4 @@
-"""BASELINE.json configs[3] and configs[4] (first half) through the request scheduler on one GPU, on
+"""The prefix-reuse workload and the admission-wave workload through the request scheduler on one GPU, on
 synthetic token ids and seeded q/k/v tables (no model):
 
   shared   256 requests = common 1024-id prefix + unique 256-id suffix (Qwen3-8B attention

@@ -184,7 +184,7 @@ def test_sin_cos_cache_close_to_cpu_table(native_libs, oracle):
 
 
 def test_config1_reference_layout_decode_fp32(native_libs, oracle):
-    """BASELINE.json configs[0] on the GPU through the reference's own cache layout: 12 Q / 2 KV
+    """The CPU-runnable anchor case (Qwen2.5-1.5B attention shape, 512 cached + 1 new token) on the GPU through the reference's own cache layout: 12 Q / 2 KV
     heads, d=128, 512 cached + 1 new token, fp32, contiguous cache, device-resident pos."""
     import torch
     from orinmllm_b200 import capi

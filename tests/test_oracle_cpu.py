@@ -6,7 +6,7 @@ from tests import kvtest
 
 
 def _config1(oracle, seed=1):
-    """BASELINE.json configs[0]: Qwen2.5-1.5B attention shape, 512 cached tokens + 1 new, fp32."""
+    """The CPU-runnable anchor case: Qwen2.5-1.5B attention shape, 512 cached tokens + 1 new, fp32."""
     H, HKV, D, S = 12, 2, 128, 520
     rng = np.random.default_rng(seed)
     kc = np.zeros((1, S, HKV * D), np.float32)

@@ -104,7 +104,7 @@ def test_free_list_is_the_seeded_permutation(kvm_mod):
 
 
 def test_config4_block_accounting(kvm_mod):
-    """BASELINE.json configs[3] at full size on the host: 256 requests share a 1024-id prefix and add
+    """The prefix-reuse workload at full size on the host: 256 requests share a 1024-id prefix and add
     256 unique ids, then 128 decode tokens each.  Aligned sizes: 64 shared blocks, no COW.
     Unaligned variant (prefix 1000 + suffix 280): the 63rd block is shared partially and every
     request copies it on its first append."""

@@ -98,7 +98,7 @@ def test_prefill_qwen3_shape(native_libs, oracle):
 
 
 def test_prefill_config3_shape_reduced(native_libs, oracle):
-    # BASELINE.json configs[2] shape (28 Q / 4 KV heads, d=128, bf16, chunks of 512, block 16) with
+    # Qwen2.5-7B attention shape (28 Q / 4 KV heads, d=128, bf16, chunks of 512, block 16) with
     # 2 sequences of 1024 tokens so the CPU oracle finishes in seconds
     worst = _run_chunked(oracle, "bf16", 28, 4, [1024, 1024], chunk=512, seed=5)
     print("config-3 (reduced) prefill parity: max_abs=%.3e max_rel=%.3e" % worst)

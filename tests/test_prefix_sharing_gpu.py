@@ -1,4 +1,4 @@
-"""Prefix-cache block sharing end to end on the GPU (BASELINE.json configs[3] pattern, reduced):
+"""Prefix-cache block sharing end to end on the GPU (the shared-prefix request pattern, reduced):
 requests sharing a common prefix map its blocks by reference through the radix tree, the
 partly filled last shared block is copied on first write (all layers, device kernel), block
 reference counts are mirrored on the device, and every request's attention output equals the
