@@ -565,8 +565,6 @@ def run_gpu(args):
                         fused=args.fused, world=world)
     if args.variant:
         wl.capi.lib().kpx_internal_set_decode_variant(args.variant)
-    if args.waves:
-        wl.capi.lib().kpx_internal_set_decode_waves(args.waves)
 
     def barrier():
         if world > 1:
@@ -722,8 +720,9 @@ def run_gpu(args):
 
 # dram bytes (read+write) / algorithmic bytes of one decode launch, from the ncu capture
 # summarised in profiles/ (same kernel, same shape, one layer)
-TRAFFIC_RATIO = 1.017
-TRAFFIC_NOTE = "ncu dram__bytes_read+write of one launch at this shape / algorithmic bytes = 1.017"
+TRAFFIC_RATIO = 1.020
+TRAFFIC_NOTE = ("ncu dram__bytes_read+write of one launch of the overlapped form at this shape / algorithmic "
+                "bytes = 534.90 MB / 524.59 MB = 1.020 (the one-CTA-per-SM form: 1.017)")
 
 
 def main():
@@ -737,7 +736,6 @@ def main():
     ap.add_argument("--fused", action="store_true",
                     help="one launch per layer (kpx_rope_append_decode) instead of kpx_rope_append + kpx_paged_decode")
     ap.add_argument("--variant", type=int, default=0, help="decode tuning variant (experiments)")
-    ap.add_argument("--waves", type=int, default=0, help="waves of CTAs per overlapped decode launch (experiments)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the prefill / append / prefix-reuse measurements after the headline")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel separately instead of replaying CUDA graphs")

@@ -13,7 +13,6 @@ int g_decode_variant = 0;
 // g_min_blocks_per_range blocks while at least g_min_warps_per_sm warps per SM stay active.
 int g_small_below = 12, g_min_blocks_per_range = 12, g_min_warps_per_sm = 4;
 // Test-only: polls before a bounded wait gives up, and the warp whose first tile never comes.
-int g_decode_waves = 0;
 uint32_t g_wait_limit = kWaitLimit;
 int g_withhold_worker = -1;
 }  // namespace decode
@@ -24,9 +23,6 @@ using namespace kpx::decode;
 
 extern "C" __attribute__((visibility("default"))) void kpx_internal_set_decode_variant(int v) {
   g_decode_variant = v;
-}
-extern "C" __attribute__((visibility("default"))) void kpx_internal_set_decode_waves(int waves) {
-  g_decode_waves = waves;
 }
 extern "C" __attribute__((visibility("default"))) void kpx_internal_set_decode_small(int below, int min_blocks,
                                                                                        int min_warps) {
@@ -45,7 +41,7 @@ extern "C" __attribute__((visibility("default"))) void kpx_internal_set_decode_f
 
 namespace {
 constexpr int64_t kSlotBytes = (4 * kD + 8) * sizeof(float);
-// what one wave needs: the least a workspace may hold (the built-in scratch is this size)
+// (the built-in scratch of kpx_paged_decode_static is this size for its head-layout limit)
 int64_t min_workspace_bytes(int32_t num_q_heads, int32_t num_kv_heads) {
   return int64_t(kStatusBytes) + counter_bytes(num_q_heads, num_kv_heads) + int64_t(kMinPartialSlots) * kSlotBytes;
 }
@@ -56,10 +52,9 @@ extern "C" int64_t kpx_decode_workspace_bytes(int32_t batch, int32_t num_q_heads
   (void)batch;
   if (num_q_heads <= 0 || num_kv_heads <= 0 || head_size != kD || num_q_heads % num_kv_heads)
     return -1;
-  // header + one counter per item of a launch + 2 partial slots per range of the line (a
-  // warp's, times the waves a launch may use), each up to 4 heads x (128 + 2) floats
-  return min_workspace_bytes(num_q_heads, num_kv_heads) +
-         int64_t(kMaxWaves - 1) * kMinPartialSlots * kSlotBytes;
+  // header + one counter per item of a launch + 2 partial slots per persistent warp,
+  // each up to 4 heads x (128 + 2) floats
+  return min_workspace_bytes(num_q_heads, num_kv_heads);
 }
 
 extern "C" int kpx_paged_decode(void* out, const void* q, const void* k_pool, const void* v_pool,
@@ -154,12 +149,7 @@ int kpx::decode_rows(void* out, const void* q, const void* k_pool, const void* v
   p.num_kv_heads = layout->num_kv_heads;
   p.kv_mul = num_q_heads / layout->num_kv_heads;
   p.head_groups = 1;
-  {
-    // slots the workspace really holds (a workspace of the documented size has room for kMaxWaves)
-    const int64_t room = (workspace_bytes - kStatusBytes - counter_bytes(num_q_heads, layout->num_kv_heads)) / kSlotBytes;
-    const int64_t cap = int64_t(kMinPartialSlots) * kMaxWaves;
-    p.partial_slots = int32_t(room < cap ? room : cap);
-  }
+  p.partial_slots = kMinPartialSlots;
   p.tile_contig = tile_contiguous(layout) ? 1 : 0;
   p.min_blocks_per_range = g_min_blocks_per_range;
   p.min_warps_per_sm = g_min_warps_per_sm;
@@ -206,7 +196,7 @@ constexpr int kStaticMaxItemsPerSeq = 16;  // num_kv_heads * head groups, e.g. 8
 constexpr int64_t kStaticCounterBytes = 65536;  // >= kMaxBatch * kStaticMaxItemsPerSeq counters
 static_assert(int64_t(kMaxBatch) * kStaticMaxItemsPerSeq * 4 <= kStaticCounterBytes, "counter area");
 constexpr int64_t kStaticScratchBytes =
-    kStatusBytes + kStaticCounterBytes + int64_t(kMinPartialSlots) * kSlotBytes;  // 10 715 392 bytes: one wave
+    kStatusBytes + kStaticCounterBytes + int64_t(kMinPartialSlots) * kSlotBytes;  // 10 715 392 bytes
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 }  // namespace
 }  // namespace kpx

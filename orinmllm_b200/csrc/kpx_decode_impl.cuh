@@ -958,12 +958,7 @@ inline int heads_per_warp(int kv_mul) {
 
 constexpr int kMaxSms = 160;  // upper bound used to size the workspace
 constexpr int kMaxWarpsPerCta = 16;
-// The small-CTA forms may launch several waves of CTAs (grid = resident CTAs x waves) so that the
-// hardware hands the later waves' ranges to whichever SM frees a slot first; every range needs
-// its two partial slots, so the workspace is sized for kMaxWaves.
-constexpr int kMaxWaves = 3;
-constexpr int kMinPartialSlots = 2 * kMaxSms * kMaxWarpsPerCta;  // one wave (also the built-in scratch)
-inline int64_t partial_slots_needed(int64_t warps) { return 2 * warps + 2 * ((warps + 15) / 16) + 1; }
+constexpr int kMinPartialSlots = 2 * kMaxSms * kMaxWarpsPerCta;  // two per warp of the largest grid
 constexpr int kStatusBytes = 256;
 
 // Tuning knob: 0 = default shape; set through kpx_internal_set_decode_variant.
@@ -972,7 +967,6 @@ extern int g_decode_variant;
 // is below g_small_below blocks per warp of the grid; then ranges hold at least
 // g_min_blocks_per_range blocks while at least g_min_warps_per_sm warps per SM stay active.
 extern int g_small_below, g_min_blocks_per_range, g_min_warps_per_sm;
-extern int g_decode_waves;  // 0: the form's default
 extern uint32_t g_wait_limit;
 extern int g_withhold_worker;
 
@@ -1011,13 +1005,6 @@ int launch_decode_form(DecodeParams p, cudaStream_t stream) {
   int grid = device_info().sm_count;
   if (grid > kMaxSms) grid = kMaxSms;
   grid *= CPS;
-  if (CPS > 1 && !kSmall) {
-    // several CTAs per SM: cut the line into `waves` times as many ranges as warps are resident
-    int waves = g_decode_waves > 0 ? g_decode_waves : 1;
-    if (waves > kMaxWaves) waves = kMaxWaves;
-    while (waves > 1 && partial_slots_needed(int64_t(grid) * waves * NW) > p.partial_slots) --waves;
-    grid *= waves;
-  }
   p.head_groups = (p.kv_mul + QH - 1) / QH;
   kern<<<grid, C::kThreads, smem_bytes, stream>>>(p);
   KPX_CUDA_TRY(cudaGetLastError());
