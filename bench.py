@@ -323,21 +323,23 @@ def _median_ms(torch, fn, reps, flush=None):
     return float(np.median(ms))
 
 
-def extra_prefill(torch, capi):
+def extra_prefill(torch, capi, dt=None):
     """Chunked prefill at the Qwen2.5-7B attention shape (28 Q / 4 KV heads, d 128, bf16, block 16):
     4 sequences of 2048-token prompts in 512-token chunks, seeded random block placement.  Device
     time of the four chunk calls of a layer (each queued several times back to back behind a
-    filler kernel, CUDA events around the queue), FLOPs counted causal-exact."""
+    filler kernel, CUDA events around the queue), FLOPs counted causal-exact.  The same with fp16
+    pools (one 16-bit term for the softmax weights instead of two) is reported under "fp16"."""
     H, HKV, D, BS, B, PROMPT, CHUNK = 28, 4, HEAD, BLOCK, 4, 2048, 512
     rng = np.random.default_rng(3)
     nb = int(B * PROMPT / BS * 1.25)
     table = rng.permutation(nb).astype(np.int32)[:B * PROMPT // BS].reshape(B, PROMPT // BS).copy()
-    dt = torch.bfloat16
+    first = dt is None
+    dt = torch.bfloat16 if dt is None else dt
     kp = torch.randn(nb, HKV, BS, D, device="cuda", dtype=dt)
     vp = torch.randn(nb, HKV, BS, D, device="cuda", dtype=dt)
     q = torch.randn(B * CHUNK, H * D, device="cuda", dtype=dt)
     out = torch.empty_like(q)
-    lay = capi.layout_paged(capi.KPX_BF16, HKV, D, BS, nb)
+    lay = capi.layout_paged(capi.dtype_code(dt), HKV, D, BS, nb)
     bt = torch.from_numpy(table).cuda()
     cu = (np.arange(B + 1) * CHUNK).astype(np.int32)
     nbytes = capi.prefill_workspace_bytes(B * CHUNK, H, HKV, D)
@@ -366,10 +368,16 @@ def extra_prefill(torch, capi):
     status = capi.workspace_status(ws)
     peak, src = tensor_peak()
     tflops = sum(flops) / total_ms / 1e9
-    return {"workload": "chunked prefill, 28 Q / 4 KV heads, bf16, 4 x 2048 tokens in chunks of 512",
-            "kernel": "prefill_tc_kernel", "tflops": round(tflops, 1), "frac_of_sustained": round(tflops / peak, 4),
-            "peak_tflops": peak, "peak_source": src, "us_per_layer": round(total_ms * 1e3, 1),
-            "flops_per_layer": sum(flops), "launches": queued * nch, "status": status}
+    res = {"workload": "chunked prefill, 28 Q / 4 KV heads, %s, 4 x 2048 tokens in chunks of 512" % (
+               "bf16" if dt == torch.bfloat16 else "fp16"),
+           "kernel": "prefill_tc_kernel", "tflops": round(tflops, 1), "frac_of_sustained": round(tflops / peak, 4),
+           "peak_tflops": peak, "peak_source": src, "us_per_layer": round(total_ms * 1e3, 1),
+           "flops_per_layer": sum(flops), "launches": queued * nch, "status": status}
+    if first:
+        del kp, vp, q, out, ws, filler
+        res["fp16"] = {k: v for k, v in extra_prefill(torch, capi, torch.float16).items()
+                       if k in ("tflops", "frac_of_sustained", "us_per_layer", "status")}
+    return res
 
 
 def extra_append(torch, capi):

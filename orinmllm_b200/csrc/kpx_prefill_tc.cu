@@ -76,6 +76,10 @@ struct PrefillParams {
   int64_t num_blocks;
   int32_t max_blocks_per_seq, num_q_heads, kv_mul;
   float qscale;  // softmax scale * log2(e)
+  // Polls a bounded wait makes before it gives up (kWaitLimit), and, for the test of that path
+  // only, the CTA whose first K tile is announced to its barrier but never requested (-1: none).
+  uint32_t wait_limit;
+  int32_t withhold_cta;
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------------
@@ -227,8 +231,9 @@ __device__ __forceinline__ bool softmax_sync_or(int id, bool pred) {
   return out != 0;
 }
 // Bounded wait that also gives up as soon as another role of the CTA has given up.
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                              uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 64) {
       __nanosleep(64);
@@ -296,9 +301,19 @@ __device__ __forceinline__ void tmem_st8(uint32_t addr, const uint32_t* r) {
                : "memory");
 }
 
+// How many 16-bit terms carry a weight p into the P V product.  One term was measured for both
+// formats and fails the output tolerance on short sequences: bf16 (2^-9 relative rounding) by a
+// few 1e-3 absolute, fp16 (2^-11) within 2e-3 absolute but up to 2.5e-2 relative on outputs near
+// zero (a 37-token sequence, where a few weights carry the row and their rounding errors do not
+// average out), against a bound of 1e-2.  Both formats therefore carry p = P_hi + P_lo and run
+// P V twice; the single-term form stays behind this constant (it is 12 % faster: 224 against
+// 250 us per layer on 4 x 2048 tokens) for a caller whose tolerance allows it.
+template <typename T>
+struct PTerms { static constexpr int kCount = 2; };
+
 // Weights of 32 keys: p = exp2(s * qscale - m), written back over the 32 columns of S they came
-// from as P_hi (columns 0..15, two keys each) and P_lo = p - P_hi (columns 16..31); lsum += p.
-// Sixteen keys at a time to keep the live registers down.
+// from as P_hi (columns 0..15, two keys each) and, with two terms, P_lo = p - P_hi (columns
+// 16..31); lsum += p.  Sixteen keys at a time to keep the live registers down.
 template <typename T, bool kMasked>
 __device__ __forceinline__ void weights32(uint32_t taddr, const uint32_t* r, float qscale, float neg_m, int limit,
                                           float2& lsum) {
@@ -318,11 +333,13 @@ __device__ __forceinline__ void weights32(uint32_t taddr, const uint32_t* r, flo
       lsum = __fadd2_rn(lsum, w);
       const uint32_t hw = pack2<T>(w.x, w.y);
       hi[i] = hw;
-      const float2 d = __ffma2_rn(make_float2(unpack_lo<T>(hw), unpack_hi<T>(hw)), m1, w);
-      lo[i] = pack2<T>(d.x, d.y);
+      if (PTerms<T>::kCount == 2) {
+        const float2 d = __ffma2_rn(make_float2(unpack_lo<T>(hw), unpack_hi<T>(hw)), m1, w);
+        lo[i] = pack2<T>(d.x, d.y);
+      }
     }
     tmem_st8(taddr + h * 8, hi);
-    tmem_st8(taddr + 16 + h * 8, lo);
+    if (PTerms<T>::kCount == 2) tmem_st8(taddr + 16 + h * 8, lo);
   }
 }
 
@@ -570,12 +587,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int kv = 0; kv < 2; ++kv) {
         uint64_t* full = (kv ? v_full : k_full) + stage;
         uint64_t* free_bar = (kv ? v_free : k_free) + stage;
-        if (use > 0) ok = ok && wait_or_abort(free_bar, uint32_t((use - 1) & 1), abort_flag);
+        if (use > 0) ok = ok && wait_or_abort(free_bar, uint32_t((use - 1) & 1), abort_flag, p.wait_limit);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         if (lane == 0) mbar_arrive_expect_tx(full, uint32_t(nblk) * (kBS * kD * 2));
         __syncwarp();
-        if (lane < 2 * nblk) {
+        const bool withheld = int(blockIdx.x) == p.withhold_cta && j == 0 && kv == 0;  // test knob
+        if (lane < 2 * nblk && !withheld) {
           uint8_t* dst = (kv ? sV : sK) + stage * kOperandB + (lane & 1) * kChunkB + (lane >> 1) * (kBS * 128);
           tma_load_4d(dst, kv ? &map_v : &map_k, (lane & 1) * 64, 0, pd.kvh, id, full);
         }
@@ -583,7 +601,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (ok && ragged && j0 + j == tilesB - 1) {
         // V rows past the newest token must be zero (a weight of 0 times pool garbage must stay
         // 0); the boxes have to land first because the last one covers some of these rows
-        ok = wait_or_abort(v_full + stage, uint32_t(use & 1), abort_flag);
+        ok = wait_or_abort(v_full + stage, uint32_t(use & 1), abort_flag, p.wait_limit);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
           uint8_t* v = sV + stage * kOperandB;
@@ -618,11 +636,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       umma_commit(s_full + x);
     };
-    // O_x += P_hi V(j) + P_lo V(j).  A = P from tensor memory: keys 16s.. of every row sit in 8
-    // columns; B = V: key rows 16s.., d along MN.  A and B of one MMA must have the same 16-bit
-    // format (an fp16 P against a bf16 V is an illegal instruction).  A single 16-bit P (2^-9
-    // rounding for bf16, 2^-12 for fp16) costs up to a few 1e-3 absolute on short sequences,
-    // beyond the 2e-3 / 1e-2 output tolerance, hence the two terms.
+    // O_x += P_hi V(j) (+ P_lo V(j) where P has two terms, see PTerms).  A = P from tensor
+    // memory: keys 16s.. of every row sit in 8 columns; B = V: key rows 16s.., d along MN.  A and
+    // B of one MMA must have the same 16-bit format (an fp16 P against a bf16 V is an illegal
+    // instruction).
     auto issue_pv = [&](int x, int j) {
       const uint32_t tP = tm + x * 128, tO = tm + 256 + x * 128;
       const uint64_t b = dv0 + uint64_t(j & 1) * kNextOperand;
@@ -630,12 +647,14 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int s = 0; s < 8; ++s)
         umma_f16_ts(tO, tP + (s >> 1) * 32 + (s & 1) * 8, b + uint64_t((s * 16 * 128) >> 4), kIdescPV,
                     (j > 0 || s > 0) ? 1u : 0u);
+      if (PTerms<T>::kCount == 2) {
 #pragma unroll
-      for (int s = 0; s < 8; ++s)
-        umma_f16_ts(tO, tP + (s >> 1) * 32 + 16 + (s & 1) * 8, b + uint64_t((s * 16 * 128) >> 4), kIdescPV, 1u);
+        for (int s = 0; s < 8; ++s)
+          umma_f16_ts(tO, tP + (s >> 1) * 32 + 16 + (s & 1) * 8, b + uint64_t((s * 16 * 128) >> 4), kIdescPV, 1u);
+      }
     };
     auto wait = [&](uint64_t* bar, int parity) {
-      ok = ok && __all_sync(0xffffffffu, wait_or_abort(bar, uint32_t(parity), abort_flag));
+      ok = ok && __all_sync(0xffffffffu, wait_or_abort(bar, uint32_t(parity), abort_flag, p.wait_limit));
       tc_fence_after();
       return ok;
     };
@@ -707,7 +726,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       RowState st;
       bool failed = false;
       auto wait_all = [&](uint64_t* bar, int parity) {
-        const bool bad = !wait_or_abort(bar, uint32_t(parity), abort_flag);
+        const bool bad = !wait_or_abort(bar, uint32_t(parity), abort_flag, p.wait_limit);
         if (softmax_sync_or(bar_id, bad)) failed = true;
         tc_fence_after();
         return !failed;
@@ -771,6 +790,9 @@ bool make_map(CUtensorMap* map, int32_t dtype, const void* base, int rank, const
 
 // -1: cut underfilled calls (default); 0: never; 2..4: always, into that many parts (tests).
 int g_prefill_split = -1;
+// Test-only: polls before a bounded wait gives up, and the CTA whose first K tile never comes.
+uint32_t g_prefill_wait_limit = kWaitLimit;
+int g_prefill_withhold_cta = -1;
 
 // Host side: pair list -> workspace, tensor maps, launch.  Returns KPX_ERR_UNIMPLEMENTED when
 // the layout, dtype or scale is outside this path so that the caller can fall back to the
@@ -916,6 +938,8 @@ int prefill_tc(void* out, const void* q, const void* k_pool, const void* v_pool,
   p.num_q_heads = num_q_heads;
   p.kv_mul = kv_mul;
   p.qscale = scale * kLog2e;
+  p.wait_limit = g_prefill_wait_limit;
+  p.withhold_cta = g_prefill_withhold_cta;
   const unsigned grid = unsigned(pairs.size());
   auto launch = [&](auto kernel, std::atomic<uint64_t>* done_mask) -> int {
     // the shared-memory attribute is per device: set once per device (atomic bit mask of devices
@@ -954,5 +978,12 @@ int64_t prefill_tc_area_bytes(int32_t total_q, int32_t num_q_heads) {
 
 }  // namespace kpx
 
+// Test knob (not in the public header): makes a bounded wait of the tensor-core kernel run out
+// without a faulting or endless kernel: CTA `withhold_cta` announces its first K tile to the
+// barrier but never requests it, and the waits give up after `wait_limit` polls (0: the default).
+extern "C" __attribute__((visibility("default"))) void kpx_internal_set_prefill_fault(uint32_t wait_limit, int withhold_cta) {
+  kpx::g_prefill_wait_limit = wait_limit ? wait_limit : kpx::kWaitLimit;
+  kpx::g_prefill_withhold_cta = withhold_cta;
+}
 // Test knob (not in the public header): see g_prefill_split.
 extern "C" __attribute__((visibility("default"))) void kpx_internal_set_prefill_split(int v) { kpx::g_prefill_split = v; }

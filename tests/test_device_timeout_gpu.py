@@ -64,3 +64,51 @@ def test_decode_wait_runs_out_and_the_workspace_recovers(native_libs, oracle, fo
     again = launch(entry)
     assert capi.workspace_status(ws) == 0
     assert torch.equal(again.view(torch.uint8), good.view(torch.uint8)), "the launch after recovery differs"
+
+
+def test_prefill_wait_runs_out_and_the_next_call_is_right(native_libs, oracle):
+    """The tensor-core prefill kernel: one CTA never gets its first K tile; its roles give up in
+    step (the loader and the MMA warp on their barriers, the softmax threads by vote), tensor
+    memory is freed, the kernel returns, the status says so, and the same call made again is right."""
+    import torch
+    from orinmllm_b200 import capi
+    H, HKV, D, n, start = 8, 2, 128, 300, 212
+    length = start + n
+    case = kvtest.make_paged_case(13, "bf16", H, HKV, [length])
+    lay = capi.layout_paged(capi.KPX_BF16, HKV, D, 16, case.num_blocks)
+    kp_ref, vp_ref = kvtest.oracle_pools(oracle, case)
+    kp, vp = kvtest.to_device(kp_ref, "bf16"), kvtest.to_device(vp_ref, "bf16")
+    rng = np.random.default_rng(5)
+    q_st = kvtest.to_storage(rng.standard_normal((n, H * D)).astype(np.float32), "bf16")
+    dq = kvtest.to_device(q_st, "bf16")
+    table = torch.from_numpy(case.block_table).cuda()
+    nbytes = capi.prefill_workspace_bytes(n, H, HKV, D)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    capi.workspace_init(ws, nbytes)
+    cu, sp = np.array([0, n], np.int32), np.array([start], np.int32)
+
+    def call():
+        out = torch.full_like(dq, float("nan"))
+        capi.paged_prefill(out, dq, kp, vp, lay, table, case.block_table.shape[1], cu, sp, 1, H, 1 / np.sqrt(D), ws, nbytes)
+        return out
+
+    kc = kvtest.storage_to_f32(oracle.gather_paged(kp_ref, case.block_table[0], length, HKV, D, 16), "bf16")
+    vc = kvtest.storage_to_f32(oracle.gather_paged(vp_ref, case.block_table[0], length, HKV, D, 16), "bf16")
+    ref = oracle.mha_prefill(start, kvtest.storage_to_f32(q_st, "bf16"), H, length, HKV * D, H // HKV, D,
+                             kc.reshape(-1), vc.reshape(-1), threads=oracle.max_threads())
+    lib = capi.lib()
+    lib.kpx_internal_set_prefill_fault(3000, 0)
+    try:
+        broken = call()
+        torch.cuda.synchronize()  # the kernel has returned
+    finally:
+        lib.kpx_internal_set_prefill_fault(0, -1)
+    assert capi.workspace_status(ws) == capi.KPX_ERR_DEVICE_TIMEOUT
+    # the withheld CTA's rows are missing: NaN where it owned them outright, wrong (its share of
+    # the keys left out) where the call was cut along the keys and merged
+    b = broken.float().cpu().numpy()
+    assert np.isnan(b).any() or np.nanmax(np.abs(b - ref)) > 10 * kvtest.ATOL
+    good = call()
+    assert capi.workspace_status(ws) == 0
+    got = kvtest.storage_to_f32(kvtest.from_device(good, "bf16"), "bf16")
+    kvtest.assert_attention_close(got, ref, "prefill after a timed-out call", "bf16")
