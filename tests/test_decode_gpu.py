@@ -102,6 +102,18 @@ def test_decode_headline_shape(native_libs, oracle):
     print(f"headline parity: max_abs={max_abs:.3e} max_rel={max_rel:.3e}")
 
 
+@pytest.mark.parametrize("dtype,heads", [("f16", (28, 4)), ("bf16", (28, 4)), ("f16", (40, 8)), ("f16", (64, 8))])
+def test_decode_headline_size_five_to_eight_heads_per_kv_head(native_libs, oracle, dtype, heads):
+    # Qwen2.5-7B attention shape (28 Q / 4 KV heads: seven query heads per KV head) and its
+    # neighbours at the headline batch: served in passes of four heads (padding heads of the last
+    # pass carry a zero query and are never written)
+    rng = np.random.default_rng(77)
+    lens = rng.integers(128, 4097, size=64)
+    case = kvtest.make_paged_case(77, dtype, heads[0], heads[1], lens)
+    max_abs, max_rel = _run_case(oracle, case, launches=2)
+    print(f"{heads[0]}/{heads[1]} heads {dtype}: max_abs={max_abs:.3e} max_rel={max_rel:.3e}")
+
+
 def test_decode_placement_invariance(native_libs, oracle):
     # the same sequences through two different block placements give bit-identical outputs
     import torch
