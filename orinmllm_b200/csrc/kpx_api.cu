@@ -97,9 +97,14 @@ extern "C" int kpx_layout_contiguous(kpx_kv_layout* out, int32_t dtype, int32_t 
 }
 
 namespace {
-// Header of a workspace: word 0 = sticky status (the kernels raise it), bytes 8..15 = the size
-// kpx_workspace_init was given, so that the workspace can be wiped again without asking.
-__global__ void workspace_note_size(int64_t* header, int64_t bytes) { header[1] = bytes; }
+// Header of a workspace: word 0 = sticky status (the kernels raise it), word 1 = a mark that
+// kpx_workspace_init has been here, bytes 8..15 = the size it was given, so that the workspace
+// can be wiped again without asking (and is not, if the header is not ours).
+constexpr int32_t kWorkspaceMark = 0x4b505857;  // "KPXW"
+__global__ void workspace_note_size(int64_t* header, int64_t bytes) {
+  reinterpret_cast<int32_t*>(header)[1] = kWorkspaceMark;
+  header[1] = bytes;
+}
 
 int wipe_workspace(void* workspace, int64_t workspace_bytes, cudaStream_t s) {
   KPX_CUDA_TRY(cudaMemsetAsync(workspace, 0, size_t(workspace_bytes), s));
@@ -122,7 +127,8 @@ extern "C" int kpx_workspace_status(void* workspace, void* stream) {
   KPX_CUDA_TRY(cudaMemcpyAsync(header, workspace, sizeof(header), cudaMemcpyDeviceToHost, s));
   KPX_CUDA_TRY(cudaStreamSynchronize(s));
   const int32_t st = static_cast<int32_t>(header[0] & 0xffffffff);
-  if (st == KPX_ERR_DEVICE_TIMEOUT && header[1] >= 256) {
+  const bool ours = static_cast<int32_t>(header[0] >> 32) == kWorkspaceMark;
+  if (st == KPX_ERR_DEVICE_TIMEOUT && ours && header[1] >= 256) {
     // warps that gave up never counted their pieces: the counters in the workspace are stale and
     // the next launch would assemble at the wrong count, so the whole workspace starts over
     int rc = wipe_workspace(workspace, header[1], s);

@@ -76,6 +76,16 @@ if rank == 0:
     del kp_all, vp_all
 else:
     max_abs = max_rel = 0.0
+# ---- the many-row form of the exchange (rows in head order on every rank)
+rows = 3
+mine = torch.full((rows, hq * D), float(rank + 1), device=dev, dtype=torch.float16) + \
+    torch.arange(rows, device=dev, dtype=torch.float16)[:, None]
+wide = torch.zeros(rows, H * D, device=dev, dtype=torch.float16)
+exchange.gather(mine, wide, rows)
+torch.cuda.synchronize()
+for r in range(world):
+    want = float(r + 1) + torch.arange(rows, device=dev, dtype=torch.float16)[:, None]
+    assert torch.equal(wide[:, r * hq * D:(r + 1) * hq * D], want.expand(rows, hq * D)), "row exchange"
 ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
 t_attn, t_gather = [], []
 for _ in range(ITERS):
