@@ -145,9 +145,13 @@ class DecodeWorkload:
         for l in range(LAYERS):
             self.k_pool[l].normal_(generator=g)
             self.v_pool[l].normal_(generator=g)
-        self.q = torch.randn(LAYERS, BATCH, Q_HEADS * HEAD, generator=g, dtype=torch.float16, device=device)
-        self.k = torch.randn(LAYERS, BATCH, KV_HEADS * HEAD, generator=g, dtype=torch.float16, device=device)
-        self.v = torch.randn(LAYERS, BATCH, KV_HEADS * HEAD, generator=g, dtype=torch.float16, device=device)
+        # a layer's new q, k and v rows lie one after the other (q block, k block, v block), on the
+        # device and in the pinned host copy alike, so that a layer's rows arrive in one copy
+        nq, nkv = BATCH * Q_HEADS * HEAD, BATCH * KV_HEADS * HEAD
+        self.qkv = torch.randn(LAYERS, nq + 2 * nkv, generator=g, dtype=torch.float16, device=device)
+        self.q = self.qkv[:, :nq].unflatten(1, (BATCH, Q_HEADS * HEAD))
+        self.k = self.qkv[:, nq:nq + nkv].unflatten(1, (BATCH, KV_HEADS * HEAD))
+        self.v = self.qkv[:, nq + nkv:].unflatten(1, (BATCH, KV_HEADS * HEAD))
         self.out = torch.empty_like(self.q)
         max_pos = int(final.max()) + 1
         self.sin = torch.empty(max_pos, HEAD, dtype=torch.float32, device=device)
@@ -163,10 +167,8 @@ class DecodeWorkload:
         self.scale = 1.0 / float(np.sqrt(HEAD))
         self.launches = 0
         # host side of the end-to-end path
-        self.h_q = self.q.cpu().pin_memory()
-        self.h_k = self.k.cpu().pin_memory()
-        self.h_v = self.v.cpu().pin_memory()
-        self.h_out = torch.empty_like(self.h_q).pin_memory()
+        self.h_qkv = self.qkv.cpu().pin_memory()
+        self.h_out = torch.empty(LAYERS, BATCH, Q_HEADS * HEAD, dtype=torch.float16).pin_memory()
         self._prepare_pointers()
         torch.cuda.synchronize(device)
 
@@ -231,9 +233,7 @@ class DecodeWorkload:
     def step_e2e(self, t):
         # Q/K/V rows of the step come from pinned host memory, outputs return to it
         for l in range(LAYERS):
-            self.q[l].copy_(self.h_q[l], non_blocking=True)
-            self.k[l].copy_(self.h_k[l], non_blocking=True)
-            self.v[l].copy_(self.h_v[l], non_blocking=True)
+            self.qkv[l].copy_(self.h_qkv[l], non_blocking=True)
             self.layer(t, l)
             self.h_out[l].copy_(self.out[l], non_blocking=True)
 
@@ -276,9 +276,7 @@ class DecodeWorkload:
                 s_.wait_stream(main)
             for l in range(LAYERS):
                 with torch.cuda.stream(h2d):
-                    self.q[l].copy_(self.h_q[l], non_blocking=True)
-                    self.k[l].copy_(self.h_k[l], non_blocking=True)
-                    self.v[l].copy_(self.h_v[l], non_blocking=True)
+                    self.qkv[l].copy_(self.h_qkv[l], non_blocking=True)
                 side[l % len(side)].wait_stream(h2d)
                 ran_on = run_layer(l)
                 d2h.wait_stream(ran_on)
@@ -672,7 +670,7 @@ def run_gpu(args):
     kernels = wl.per_layer * LAYERS
     launch = ("one CUDA graph replay per step: %d kernels, layer l on chain l %% %d (layers are independent: own pool, "
               "own rows, own workspace per chain), so a layer's CTAs take the SMs the previous layer's CTAs leave; "
-              "end to end: plus 108 H2D and 36 D2H copies on side streams" % (kernels, chains)) if use_graph \
+              "end to end: plus 36 H2D and 36 D2H copies on side streams" % (kernels, chains)) if use_graph \
         else "one launch per kernel, one stream"
     line = {
         "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": K,
