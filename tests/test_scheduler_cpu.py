@@ -319,3 +319,75 @@ def test_multi_turn_histories_are_reclaimable_without_clear():
     assert m.cached_tokens == 0
     drive(s)
     assert s.state(big) == 3
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5])
+def test_random_serving_mix_always_progresses_and_conserves_blocks(seed):
+    """A soak of the host logic: random prompts (many sharing prefixes of random lengths, so
+    spans nest, split and get evicted), random generation lengths, some multi-turn requests,
+    on a pool small enough that admission has to reclaim cached spans all the time.  The loop must
+    never stall, blocks are conserved at every step, and once everything has finished the cache
+    can give every block back."""
+    rng = np.random.default_rng(seed)
+    nblocks = 96
+    m = kvm.KvManager(nblocks, BS, seed=seed)
+    s = sched.Scheduler(m, prefill_chunk=40, max_prefill_tokens=160, max_prefill_rows=6, max_decode_batch=12)
+    stems = [rng.integers(0, 151936, int(rng.integers(10, 200))) for _ in range(6)]
+    submitted, refused = [], 0
+    pending = 140
+
+    def submit_some(k):
+        nonlocal pending, refused
+        for _ in range(k):
+            if pending == 0:
+                return
+            pending -= 1
+            stem = stems[int(rng.integers(0, len(stems)))]
+            cut = int(rng.integers(1, len(stem) + 1))
+            prompt = np.concatenate([stem[:cut], rng.integers(0, 151936, int(rng.integers(1, 120)))]).astype(np.int32)
+            gen = int(rng.integers(1, 60))
+            try:
+                if rng.random() < 0.3:
+                    rid = s.submit_turn(prompt, gen, turn_suffix=list(rng.integers(0, 1000, int(rng.integers(0, 4)))),
+                                        also_register=cut if rng.random() < 0.5 else 0)
+                else:
+                    rid = s.submit(prompt, gen, also_register=cut if rng.random() < 0.5 else 0)
+                submitted.append(rid)
+            except ValueError:
+                refused += 1  # larger than the whole pool
+
+    def check_conservation(_=None):
+        counts = m.ref_counts()
+        assert m.num_free == int((counts == 0).sum()), "free list and reference counts disagree"
+        assert counts.min() >= 0
+
+    submit_some(20)
+    steps = 0
+    while s.num_waiting or s.num_running or pending:
+        submit_some(int(rng.integers(0, 4)))
+        s.admit()
+        progressed = False
+        while True:
+            p = s.next_prefill()
+            if p is None:
+                break
+            progressed = True
+            check_conservation()
+            s.complete_prefill([int(rng.integers(0, 151936)) for _ in p.request_ids])
+        d = s.next_decode()
+        if d is not None:
+            progressed = True
+            check_conservation()
+            s.complete_decode([int(rng.integers(0, 151936)) for _ in d.request_ids])
+        steps += 1
+        assert progressed or not (s.num_waiting or s.num_running), "requests outstanding and nothing runnable"
+        assert steps < 20000
+    st = s.stats()
+    assert st["finished"] == len(submitted) and st["finished"] + refused == 140
+    assert st["reused_tokens"] > 0 and st["admission_stalls"] > 0
+    check_conservation()
+    # everything has finished: a request as large as the pool must be admissible (every span reclaimable)
+    big = s.submit(np.arange(700000, 700000 + 100, dtype=np.int32), nblocks * BS - 100 + 1)
+    assert s.admit() == 1
+    drive(s)
+    assert s.state(big) == 3
