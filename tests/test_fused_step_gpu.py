@@ -128,3 +128,52 @@ def test_fused_step_rejects_bad_arguments(native_libs):
     assert lib.kpx_rope_append_decode(*args(None, 0)) == capi.KPX_ERR_INVALID_ARGUMENT
     assert lib.kpx_rope_append_decode(*args(capi.ptr(t), 6)) == capi.KPX_ERR_INVALID_ARGUMENT
     assert lib.kpx_rope_append_decode(*args(capi.ptr(t) + 2, 0)) == capi.KPX_ERR_INVALID_ARGUMENT
+
+
+def test_fused_step_many_sequences_in_slices(native_libs, oracle):
+    """More sequences than one launch's prefix table holds: the entry point slices the batch, and
+    every slice must pick up its own rows of q / k_new / v_new / positions."""
+    rng = np.random.default_rng(3)
+    _run(oracle, "f16", (8, 2), rng.integers(0, 70, size=700), seed=33)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16"])
+def test_fused_step_reference_cache_layout(native_libs, oracle, dtype):
+    """The reference's own cache [seq_len][kv_dim] (token-major, no block table, batch 1): the step
+    rotates q and k, stores row `pos` of the K and V caches and attends rows 0..pos, which is
+    RoPEGpuPosLayer -> KVCacheLayer x2 -> MHAGpuPosLayer in one launch."""
+    import torch
+    from orinmllm_b200 import capi
+    H, HKV, D, S, pos = 12, 2, 128, 544, 512
+    kv_dim = HKV * D
+    rng = np.random.default_rng(12)
+    kc = kvtest.to_storage(rng.standard_normal((S, kv_dim)).astype(np.float32), dtype)
+    vc = kvtest.to_storage(rng.standard_normal((S, kv_dim)).astype(np.float32), dtype)
+    q = kvtest.to_storage(rng.standard_normal((1, H * D)).astype(np.float32), dtype)
+    kn = kvtest.to_storage(rng.standard_normal((1, kv_dim)).astype(np.float32), dtype)
+    vn = kvtest.to_storage(rng.standard_normal((1, kv_dim)).astype(np.float32), dtype)
+    sin, cos = oracle.sin_cos_cache(D, S, 1e6)
+    # CPU statement: rotate, store row pos, attend 0..pos over the contiguous cache
+    q_rot, k_rot = kvtest.storage_to_f32(q, dtype).copy(), kvtest.storage_to_f32(kn, dtype).copy()
+    oracle.rope(pos, q_rot[0], k_rot[0], D, sin, cos)
+    q_rot = kvtest.storage_to_f32(kvtest.to_storage(q_rot, dtype), dtype)
+    kc_ref, vc_ref = kc.copy(), vc.copy()
+    kc_ref[pos] = kvtest.to_storage(k_rot, dtype)[0]
+    vc_ref[pos] = vn[0]
+    ref = oracle.mha(pos, H, 0, S, kv_dim, H // HKV, D, q_rot[0], kvtest.storage_to_f32(kc_ref, dtype).reshape(-1),
+                     kvtest.storage_to_f32(vc_ref, dtype).reshape(-1))
+    lay = capi.layout_contiguous(capi.dtype_code(kvtest.torch_dtype(dtype)), HKV, D, 16, S // 16)
+    dk, dv = kvtest.to_device(kc, dtype), kvtest.to_device(vc, dtype)
+    dq, dkn, dvn = kvtest.to_device(q, dtype), kvtest.to_device(kn, dtype), kvtest.to_device(vn, dtype)
+    out = torch.full_like(dq, float("nan"))
+    nbytes = capi.decode_workspace_bytes(1, H, HKV)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    capi.workspace_init(ws, nbytes)
+    d_pos = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    capi.rope_append_decode(out, dq, dkn, dvn, torch.from_numpy(sin).cuda(), torch.from_numpy(cos).cuda(), dk, dv, lay,
+                            None, 0, d_pos, 1, H, 1 / np.sqrt(D), ws, nbytes, 0)
+    assert capi.workspace_status(ws) == 0
+    assert np.array_equal(kvtest.from_device(dk, dtype).view(np.uint8), kc_ref.view(np.uint8))
+    assert np.array_equal(kvtest.from_device(dv, dtype).view(np.uint8), vc_ref.view(np.uint8))
+    got = kvtest.storage_to_f32(kvtest.from_device(out, dtype), dtype)
+    kvtest.assert_attention_close(got[0], ref, f"fused step, reference layout {dtype}", dtype)
