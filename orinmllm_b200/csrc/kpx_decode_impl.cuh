@@ -124,15 +124,30 @@ struct Cursor {
   __device__ __forceinline__ void locate(const DecodeParams& p, const int* prefix, int64_t u) {
     const int per_seq = p.num_kv_heads * p.head_groups;
     int lo = 0, hi = p.batch;  // first b with prefix[b+1]*per_seq > u
-    while (lo < hi) {
-      int mid = (lo + hi) >> 1;
-      if (int64_t(prefix[mid + 1]) * per_seq > u) hi = mid; else lo = mid + 1;
+    if (int64_t(prefix[p.batch]) * per_seq < (int64_t(1) << 31)) {
+      // the whole line fits 31 bits (every launch but the very largest): 32-bit compares and one
+      // 32-bit division instead of 64-bit ones; this runs before a warp's first tile request
+      const uint32_t u32 = uint32_t(u), ps = uint32_t(per_seq);
+      while (lo < hi) {
+        int mid = (lo + hi) >> 1;
+        if (uint32_t(prefix[mid + 1]) * ps > u32) hi = mid; else lo = mid + 1;
+      }
+      b = lo;
+      nblk = prefix[b + 1] - prefix[b];
+      const uint32_t r = u32 - uint32_t(prefix[b]) * ps;
+      sub = int(r / uint32_t(nblk));
+      blk = int(r - uint32_t(sub) * uint32_t(nblk));
+    } else {
+      while (lo < hi) {
+        int mid = (lo + hi) >> 1;
+        if (int64_t(prefix[mid + 1]) * per_seq > u) hi = mid; else lo = mid + 1;
+      }
+      b = lo;
+      nblk = prefix[b + 1] - prefix[b];
+      int64_t r = u - int64_t(prefix[b]) * per_seq;
+      sub = int(r / nblk);
+      blk = int(r - int64_t(sub) * nblk);
     }
-    b = lo;
-    nblk = prefix[b + 1] - prefix[b];
-    int64_t r = u - int64_t(prefix[b]) * per_seq;
-    sub = int(r / nblk);
-    blk = int(r - int64_t(sub) * nblk);
     len = seq_len_of(p, b);
     refresh(p);
   }
@@ -315,7 +330,11 @@ paged_decode_kernel(const DecodeParams p) {
   const int64_t W = W_;
   const int64_t worker = worker_;
   Split split;
-  split.quot = total / W;
+  if (total < (int64_t(1) << 31)) {  // (W is at most a few thousand)
+    split.quot = int64_t(uint32_t(total) / uint32_t(W));
+  } else {
+    split.quot = total / W;
+  }
   split.rem = total - split.quot * W;
   const int64_t u0 = split.start(worker), u1 = split.start(worker + 1);
   if (u0 >= u1) return;  // nothing below synchronises across warps
@@ -338,8 +357,24 @@ paged_decode_kernel(const DecodeParams p) {
   // is requested when a K slot frees up; its V tile is requested one step later (the
   // output pass trails the score pass by one block), reusing the source offset and
   // row count remembered from the K request.
-  Cursor pc;
-  pc.locate(p, prefix, u0);
+  Cursor cur;  // consumer side: first block of the current segment
+  cur.locate(p, prefix, u0);
+  // The first item's query rows are requested here, before the first block id and the first
+  // tiles, so that their latency (DRAM if nothing brought them to L2) runs under those.
+  uint4 q_first[kFused ? 1 : QH][kFused ? 1 : NCH];
+  if constexpr (!kFused) {
+    const int hg0 = cur.sub - cur.kvh * p.head_groups;
+    const T* qrow0 = static_cast<const T*>(p.q) + int64_t(cur.b) * p.num_q_heads * kD;
+#pragma unroll
+    for (int j = 0; j < QH; ++j) {
+      const int hq = hg0 * QH + j;
+      const T* qh = qrow0 + int64_t(cur.kvh * p.kv_mul + (hq < p.kv_mul ? hq : 0)) * kD;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c)
+        q_first[j][c] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(qh) + coff[c]));
+    }
+  }
+  Cursor pc = cur;      // producer side: walks the range NS blocks ahead
   int pc_id;            // block id at pc (loaded one step before it is needed)
   int64_t last_off = 0; // byte offset of the last requested block's (block, kv head) tile
   int last_rows = kBS;  // its number of existing rows (strided layout only)
@@ -391,14 +426,14 @@ paged_decode_kernel(const DecodeParams p) {
   }
 
   // ---- consumer state ----
-  Cursor cur;  // first block of the current segment
-  cur.locate(p, prefix, u0);
   float2 q2[QH][HP];
   float2 acc[QH][HP];
   float m_run[NV], l_run[NV];
 
-  // blocks_left: blocks of the warp's range from the item's first block in it onwards
-  auto begin_item = [&](int blocks_left) {
+  // blocks_left: blocks of the warp's range from the item's first block in it onwards;
+  // first_tag: the warp's first item, whose query rows were requested in the prologue
+  auto begin_item = [&](int blocks_left, auto first_tag) {
+    constexpr bool kFirst = decltype(first_tag)::value;
     const int hg = cur.sub - cur.kvh * p.head_groups;
     const T* qrow = static_cast<const T*>(p.q) + int64_t(cur.b) * p.num_q_heads * kD;
     if constexpr (kFused) {
@@ -425,6 +460,8 @@ paged_decode_kernel(const DecodeParams p) {
         uint4 raw;
         if constexpr (kFused)  // rotated at the new token's position, rounded to T
           raw = *reinterpret_cast<const uint4*>(stage + j * (kD * C::kEltB) + coff[c]);
+        else if constexpr (kFirst)
+          raw = q_first[j][c];
         else
           raw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(qh) + coff[c]));
         Elt<T>::unpack(raw, f);
@@ -766,7 +803,7 @@ paged_decode_kernel(const DecodeParams p) {
     return true;
   };
 
-  begin_item(n);
+  begin_item(n, std::true_type{});
   int64_t item_first = u0 - cur.blk;  // global block index where the current item starts
   int ks = 0, vs = 0;                 // slots of the next K block and the next V block to consume
   uint32_t kph = 0, vph = 0;          // their phase parities
@@ -938,7 +975,7 @@ paged_decode_kernel(const DecodeParams p) {
       cur.blk += m - 1;
       cur.advance(p, prefix);
       item_first = item_end;
-      begin_item(n - i);
+      begin_item(n - i, std::false_type{});
     }
   }
 }
