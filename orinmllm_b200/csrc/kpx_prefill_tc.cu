@@ -3,15 +3,18 @@
 // One CTA = two items (128 query rows x one query head each) of one sequence that share a KV
 // head, so one stream of K/V tiles serves both.  576 threads in roles:
 //   warp 17      TMA: Q boxes, then per 128-key tile the (block, head) boxes of K and V through
-//                the block table into 128-byte-swizzled shared memory (two stages each)
+//                the block table into 128-byte-swizzled shared memory (two stages each); it also
+//                waits for the tiles to land and publishes the count in a progress word
 //   warp 16      walks the MMA schedule in step, one elected lane issues tcgen05.mma:
 //                S_x = Q_x K^T  into tensor memory (128 columns per item) and  O_x += P_x V
 //                (A = P read from tensor memory, B = V MN-major as it sits in the pool);
-//                completion is committed to mbarriers
+//                completion is committed to mbarriers.  In its loop it polls no barrier: one
+//                plain load of the progress words shows what a step needs
 //   warps 0..7   softmax of item 0, warps 8..15 softmax of item 1: S_x -> P_x = exp2(S*c - m)
 //                written over S_x as two 16-bit terms (tcgen05.ld / st; two threads per query
 //                row), causal mask on the diagonal, running maximum moved lazily, O_x rescaled
-//                in tensor memory when it moves
+//                in tensor memory when it moves; P is handed over in two waves per tile (each
+//                warp counts them in its progress word)
 // The MMA order  PV_0(j) QK_0(j+1) | PV_1(j) QK_1(j+1)  keeps the tensor core on one item while
 // the softmax threads work on the other.
 // A CTA may own only a range of its pair's key tiles (a call with too few pairs to fill the SMs
@@ -23,6 +26,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <type_traits>
 #include <vector>
 
 #include "kpx_common.cuh"
@@ -210,6 +214,7 @@ __device__ __forceinline__ float unpack_hi<__half>(uint32_t w) {
 // per SM whatever its shared-memory and register footprint, so the overlap of softmax and
 // tensor-core work has to happen inside the CTA: each CTA carries two items (A, B) and
 // alternates between them.
+constexpr int kKTilesWord = 16, kVTilesWord = 17, kAbortWord = 18;  // progress words, see the kernel
 constexpr int kMmaWarp = 16, kLoadWarp = 17;  // warps 0..7: softmax of item 0, warps 8..15: of item 1
 constexpr int kThreads = 576;
 constexpr int kSmemBytes = 1024 /*align slack*/ + 2 * kOperandB /*Q of A, B*/ + 2 * kOperandB /*K x2*/ +
@@ -295,6 +300,13 @@ __device__ __forceinline__ float max32(const uint32_t* r, int limit, float mx) {
   return mx;
 }
 
+__device__ __forceinline__ void tmem_ld8(uint32_t addr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(addr)
+               : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void tmem_st8(uint32_t addr, const uint32_t* r) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
                ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
@@ -311,36 +323,40 @@ __device__ __forceinline__ void tmem_st8(uint32_t addr, const uint32_t* r) {
 template <typename T>
 struct PTerms { static constexpr int kCount = 2; };
 
-// Weights of 32 keys: p = exp2(s * qscale - m), written back over the 32 columns of S they came
-// from as P_hi (columns 0..15, two keys each) and, with two terms, P_lo = p - P_hi (columns
-// 16..31); lsum += p.  Sixteen keys at a time to keep the live registers down.
+// P reaches the MMA warp in kWaves hand-overs per 128-key tile: a thread's 64 keys are four
+// groups of 16 (one k = 16 step of the P V product each); after every 4 / kWaves groups the warp
+// announces them, and the MMA warp issues the P V steps of that wave while the softmax threads
+// are still at the exponentials of the next one.
+constexpr int kWaves = 2;
+constexpr int kGroupsPerWave = 4 / kWaves;
+
+// Weights of 16 keys, group h (0 or 1) of a 32-column slice of S whose scores are in r[0..31]:
+// p = exp2(s * qscale - m), written over the slice as P_hi (columns 8h..8h+7, two keys each) and,
+// with two terms, P_lo = p - P_hi (columns 16+8h..); lsum += p.  Keys e > limit are masked.
 template <typename T, bool kMasked>
-__device__ __forceinline__ void weights32(uint32_t taddr, const uint32_t* r, float qscale, float neg_m, int limit,
-                                          float2& lsum) {
+__device__ __forceinline__ void weights16(uint32_t taddr, int h, const uint32_t* r, float qscale, float neg_m,
+                                          int limit, float2& lsum) {
   const float2 sc = make_float2(qscale, qscale), nm = make_float2(neg_m, neg_m), m1 = make_float2(-1.f, -1.f);
+  uint32_t hi[8], lo[8];
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    uint32_t hi[8], lo[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int e = h * 16 + 2 * i;
-      const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), sc, nm);
-      float2 w = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-      if (kMasked) {
-        if (e > limit) w.x = 0.f;
-        if (e + 1 > limit) w.y = 0.f;
-      }
-      lsum = __fadd2_rn(lsum, w);
-      const uint32_t hw = pack2<T>(w.x, w.y);
-      hi[i] = hw;
-      if (PTerms<T>::kCount == 2) {
-        const float2 d = __ffma2_rn(make_float2(unpack_lo<T>(hw), unpack_hi<T>(hw)), m1, w);
-        lo[i] = pack2<T>(d.x, d.y);
-      }
+  for (int i = 0; i < 8; ++i) {
+    const int e = h * 16 + 2 * i;
+    const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), sc, nm);
+    float2 w = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+    if (kMasked) {
+      if (e > limit) w.x = 0.f;
+      if (e + 1 > limit) w.y = 0.f;
     }
-    tmem_st8(taddr + h * 8, hi);
-    if (PTerms<T>::kCount == 2) tmem_st8(taddr + 16 + h * 8, lo);
+    lsum = __fadd2_rn(lsum, w);
+    const uint32_t hw = pack2<T>(w.x, w.y);
+    hi[i] = hw;
+    if (PTerms<T>::kCount == 2) {
+      const float2 d = __ffma2_rn(make_float2(unpack_lo<T>(hw), unpack_hi<T>(hw)), m1, w);
+      lo[i] = pack2<T>(d.x, d.y);
+    }
   }
+  tmem_st8(taddr + h * 8, hi);
+  if (PTerms<T>::kCount == 2) tmem_st8(taddr + 16 + h * 8, lo);
 }
 
 // Per-thread softmax state of one item: this thread owns (row, column half) of S and O.
@@ -353,13 +369,16 @@ struct RowState {
 // log2 units): weights stay below 2^8, and O is rescaled in far fewer tiles.
 constexpr float kLazyMax = 8.f;
 
-// Softmax of key tile j of one item: S (tensor memory, 128 columns at tS) -> P over S, O (which
-// holds something when has_o) rescaled where the row maximum moved.  Called by the 256 softmax threads of the item (contains their
-// barrier `bar_id`).
+// Softmax of key tile j of one item: S (tensor memory, 128 columns at tS) -> P over S, handed to
+// the MMA warp wave by wave (this warp's progress word counts the waves it has announced); O (which holds something when has_o) is
+// rescaled first where the row maximum moved.  Called by the 256 softmax threads of the item
+// (contains their barrier `bar_id`, which also carries the vote on `bad`: a thread whose wait for
+// S ran out).  Returns false, in all 256 threads alike, when any of them passed bad.
 template <typename T>
-__device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t lane_addr, int row, int half,
+__device__ __forceinline__ bool softmax_tile(uint32_t tS, uint32_t tO, uint32_t lane_addr, int row, int half,
                                              float qscale, int j, bool has_o, int pos0, float* s_half,
-                                             int bar_id, RowState& st) {
+                                             int bar_id, RowState& st, bool bad, volatile uint32_t* my_word,
+                                             uint32_t waves_before, int lane) {
   const int my_pos = pos0 + row;
   const bool diag = (j * kTile + kTile - 1) > pos0;  // some row of this item is masked in this tile
   const int limit0 = my_pos - (j * kTile + half * 64);   // keys e > limit are newer than the query
@@ -371,7 +390,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t 
   if (diag) mx = max32<true>(r1, limit0 - 32, max32<true>(r0, limit0, -INFINITY));
   else mx = max32<false>(r1, 0, max32<false>(r0, 0, -INFINITY));
   s_half[half * kTile + row] = mx;
-  softmax_sync(bar_id);  // the other half of the row has published its maximum
+  if (softmax_sync_or(bar_id, bad)) return false;  // the other half of the row has published its maximum
   const float m_tile = fmaxf(mx, s_half[(half ^ 1) * kTile + row]) * qscale;
   float alpha = 1.f;
   if (m_tile > st.m + kLazyMax || st.m == -INFINITY) {  // (-inf + 8 is -inf: the first tile always moves it)
@@ -381,25 +400,37 @@ __device__ __forceinline__ void softmax_tile(uint32_t tS, uint32_t tO, uint32_t 
     st.l.x *= alpha;
     st.l.y *= alpha;
   }
-  const float neg_m = -st.m;
-  if (diag) {
-    weights32<T, true>(tS + lane_addr, r0, qscale, neg_m, limit0, st.l);
-    weights32<T, true>(tS + lane_addr + 32, r1, qscale, neg_m, limit0 - 32, st.l);
-  } else {
-    weights32<T, false>(tS + lane_addr, r0, qscale, neg_m, 0, st.l);
-    weights32<T, false>(tS + lane_addr + 32, r1, qscale, neg_m, 0, st.l);
-  }
-  // O += P V of the previous tile has completed (the MMA that produced S was issued after it)
+  // O += P V of the previous tile has completed (the MMA that produced S was issued after it), and
+  // none of this tile's is issued before every warp of the item has announced its first wave
   if (has_o && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+    for (int c = 0; c < 8; ++c) {
+      uint32_t o[8];
+      tmem_ld8(tO + lane_addr + c * 8, o);
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      tmem_ld32(tO + lane_addr + c * 32, r0);
-#pragma unroll
-      for (int e = 0; e < 32; ++e) r0[e] = __float_as_uint(__uint_as_float(r0[e]) * alpha);
-      tmem_st32(tO + lane_addr + c * 32, r0);
+      for (int e = 0; e < 8; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+      tmem_st8(tO + lane_addr + c * 8, o);
     }
   }
-  tmem_wait_st();
+  const float neg_m = -st.m;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const uint32_t* r = g < 2 ? r0 : r1;
+    const uint32_t taddr = tS + lane_addr + (g >> 1) * 32;
+    const int limit = limit0 - (g >> 1) * 32;
+    if (diag) weights16<T, true>(taddr, g & 1, r, qscale, neg_m, limit, st.l);
+    else weights16<T, false>(taddr, g & 1, r, qscale, neg_m, limit, st.l);
+    if ((g + 1) % kGroupsPerWave == 0) {
+      tmem_wait_st();  // this warp's part of the wave (and a rescaled O) is in tensor memory
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_block();
+        *my_word = waves_before + uint32_t(g / kGroupsPerWave) + 1u;
+      }
+    }
+  }
+  return true;
 }
 
 // out rows of one item = O / l.  Called by the 256 softmax threads of the item (contains their
@@ -527,11 +558,14 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* k_free = bars + 5;     // [2] every MMA reading the stage has completed
   uint64_t* v_free = bars + 7;     // [2]
   uint64_t* s_full = bars + 9;     // [2] S of item x complete (and every earlier MMA)
-  uint64_t* p_full = bars + 11;    // [2] P of item x written, O rescaled (8 warps arrive)
-  uint64_t* o_full = bars + 13;    // [2] last O += P V of item x complete
-  uint64_t* tail_ok = bars + 15;   // rows past the newest token are zero in the last V tile
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
+  uint64_t* o_full = bars + 11;    // [2] last O += P V of item x complete
+  constexpr int kNumBars = 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+  // Progress words the MMA warp reads with one plain load (lane i reads word i, see there):
+  // [0..7] / [8..15] waves of P announced by the softmax warps of item 0 / 1, [16] K tiles and
+  // [17] V tiles that have landed, [18] the CTA's give-up flag.
+  volatile uint32_t* flags = reinterpret_cast<volatile uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(flags + kAbortWord);
   float* s_half = reinterpret_cast<float*>(sV + 2 * kOperandB + 256);  // [2 items][2][128]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -547,8 +581,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   const bool ragged = (kv_len % kTile) != 0;                 // the last tile has rows past the newest token
 
   if (tid == 0) {
-    for (int i = 0; i < 16; ++i) mbar_init(bars + i, (i == 11 || i == 12) ? 8u : 1u);
-    *abort_flag = 0;
+    for (int i = 0; i < kNumBars; ++i) mbar_init(bars + i, 1u);
+    for (int i = 0; i < 32; ++i) flags[i] = 0;
     mbar_fence_init();
   }
   if (warp == 0) tmem_alloc(tmem_slot, 512);
@@ -598,21 +632,27 @@ __global__ void __launch_bounds__(kThreads, 1)
           tma_load_4d(dst, kv ? &map_v : &map_k, (lane & 1) * 64, 0, pd.kvh, id, full);
         }
       }
+      // Tell the MMA warp what has landed (it reads plain words instead of polling these
+      // barriers itself: a poll of a barrier costs it about 200 clocks each time).
+      if (ok) ok = wait_or_abort(k_full + stage, uint32_t(use & 1), abort_flag, p.wait_limit);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok && lane == 0) flags[kKTilesWord] = uint32_t(j + 1);
+      if (ok) ok = wait_or_abort(v_full + stage, uint32_t(use & 1), abort_flag, p.wait_limit);
+      ok = __all_sync(0xffffffffu, ok);
       if (ok && ragged && j0 + j == tilesB - 1) {
         // V rows past the newest token must be zero (a weight of 0 times pool garbage must stay
-        // 0); the boxes have to land first because the last one covers some of these rows
-        ok = wait_or_abort(v_full + stage, uint32_t(use & 1), abort_flag, p.wait_limit);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-          uint8_t* v = sV + stage * kOperandB;
-          for (int i = left * 16 + lane; i < kTile * 16; i += 32) {  // 16-byte pieces of rows left..127
-            const int r = i >> 4, c = i & 15;
-            *reinterpret_cast<uint4*>(v + (c >> 3) * kChunkB + r * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
-          }
-          fence_async_proxy();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(tail_ok);
+        // 0); the boxes have landed, the last one covers some of these rows
+        uint8_t* v = sV + stage * kOperandB;
+        for (int i = left * 16 + lane; i < kTile * 16; i += 32) {  // 16-byte pieces of rows left..127
+          const int r = i >> 4, c = i & 15;
+          *reinterpret_cast<uint4*>(v + (c >> 3) * kChunkB + r * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
         }
+        fence_async_proxy();
+      }
+      __syncwarp();
+      if (ok && lane == 0) {
+        __threadfence_block();
+        flags[kVTilesWord] = uint32_t(j + 1);
       }
     }
   } else if (warp == kMmaWarp) {
@@ -636,21 +676,25 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       umma_commit(s_full + x);
     };
-    // O_x += P_hi V(j) (+ P_lo V(j) where P has two terms, see PTerms).  A = P from tensor
-    // memory: keys 16s.. of every row sit in 8 columns; B = V: key rows 16s.., d along MN.  A and
-    // B of one MMA must have the same 16-bit format (an fp16 P against a bf16 V is an illegal
-    // instruction).
-    auto issue_pv = [&](int x, int j) {
+    // Wave w of O_x += P_hi V(j) (+ P_lo V(j) where P has two terms, see PTerms).  A = P from
+    // tensor memory: keys 16s.. of every row sit in 8 columns; B = V: key rows 16s.., d along MN.
+    // A and B of one MMA must have the same 16-bit format (an fp16 P against a bf16 V is an
+    // illegal instruction).  The two threads of a query row own keys 0..63 and 64..127 and work
+    // through them in step, so a wave is the k steps g and g + 4 for its groups g.
+    auto issue_pv_wave = [&](int x, int j, int w) {
       const uint32_t tP = tm + x * 128, tO = tm + 256 + x * 128;
       const uint64_t b = dv0 + uint64_t(j & 1) * kNextOperand;
 #pragma unroll
-      for (int s = 0; s < 8; ++s)
-        umma_f16_ts(tO, tP + (s >> 1) * 32 + (s & 1) * 8, b + uint64_t((s * 16 * 128) >> 4), kIdescPV,
-                    (j > 0 || s > 0) ? 1u : 0u);
-      if (PTerms<T>::kCount == 2) {
+      for (int gg = 0; gg < kGroupsPerWave; ++gg) {
+        const int g = w * kGroupsPerWave + gg;
 #pragma unroll
-        for (int s = 0; s < 8; ++s)
-          umma_f16_ts(tO, tP + (s >> 1) * 32 + 16 + (s & 1) * 8, b + uint64_t((s * 16 * 128) >> 4), kIdescPV, 1u);
+        for (int hh = 0; hh < 2; ++hh) {
+          const int s = g + 4 * hh;
+          const uint32_t a = tP + (s >> 1) * 32 + (s & 1) * 8;
+          const uint64_t bs = b + uint64_t((s * 16 * 128) >> 4);
+          umma_f16_ts(tO, a, bs, kIdescPV, (j > 0 || g > 0 || hh > 0) ? 1u : 0u);
+          if (PTerms<T>::kCount == 2) umma_f16_ts(tO, a + 16, bs, kIdescPV, 1u);
+        }
       }
     };
     auto wait = [&](uint64_t* bar, int parity) {
@@ -658,13 +702,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_after();
       return ok;
     };
-    // K(j) / V(j) of stage j&1 are in their (j>>1)-th use; the last tile also waits for the zeroed tail
-    auto wait_k = [&](int j) { return wait(k_full + (j & 1), (j >> 1) & 1); };
-    auto wait_v = [&](int j) {
-      if (ragged && j0 + j == tilesB - 1 && !wait(tail_ok, 0)) return false;
-      return wait(v_full + (j & 1), (j >> 1) & 1);
-    };
-    if (wait(q_full, 0) && wait_k(0)) {
+    if (wait(q_full, 0) && wait(k_full, 0)) {
       if (elect_one()) {
         if (nA > 0) issue_qk(0, 0);
         issue_qk(1, 0);
@@ -672,38 +710,69 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       __syncwarp();
     }
-    for (int j = 0; j < nB && ok; ++j) {
-      // item 0, while the softmax threads are busy with item 1 (and the other way round below)
-      if (j < nA) {
-        if (!wait(p_full, j & 1) || !wait_v(j)) break;
-        if (elect_one()) {
-          issue_pv(0, j);
-          if (j + 1 == nA) umma_commit(o_full);
+    // This warp is one dependent instruction stream next to sixteen busy softmax warps, and what
+    // it does between two batches of MMAs is time the tensor pipe stands still.  A per-step
+    // timeline showed a poll of a barrier in shared memory to cost it about 200 clocks, complete
+    // or not (1 650 of 4 650 clocks per key tile of the pair went into polls).  So it polls no
+    // barrier in the loop: the softmax warps and the loader publish their progress in plain
+    // words, and one load, lane i reading word i, shows everything a step needs: the item's
+    // eight softmax warps (lanes 0..7), the K and V tiles landed (lanes 8, 9), the give-up flag
+    // (lane 10).  The steps are unrolled with item and wave as constants.
+    const int word_other = lane < 8 ? 0 : lane < 11 ? lane + 8 : 19;  // lanes 8..10 read words 16..18, the rest a word that stays 0
+    auto step = [&](auto item, auto wave, int j) -> bool {
+      constexpr int x = decltype(item)::value, w = decltype(wave)::value;
+      const int n_x = x ? nB : nA;
+      const bool scores_next = w + 1 == kWaves && j + 1 < n_x;
+      uint32_t need = 0;
+      if (lane < 8) need = uint32_t(j * kWaves + w + 1);
+      else if (lane == 8) need = scores_next ? uint32_t(j + 2) : 0u;
+      else if (lane == 9) need = uint32_t(j + 1);
+      const volatile uint32_t* word = flags + (lane < 8 ? x * 8 + lane : word_other);
+      bool ready = false;
+      for (uint32_t i = 0; i < p.wait_limit; ++i) {
+        const uint32_t v = *word;
+        const uint32_t good = __ballot_sync(0xffffffffu, lane == 10 ? v == 0 : v >= need);
+        if (good == 0xffffffffu) {
+          ready = true;
+          break;
         }
-        __syncwarp();
+        if (!((good >> 10) & 1u)) return false;  // another role has given up
       }
-      if (j + 1 < nA) {
-        if (!wait_k(j + 1)) break;
-        if (elect_one()) {
-          issue_qk(0, j + 1);
-        }
-        __syncwarp();
+      if (!ready) {
+        *abort_flag = 1;
+        return false;
       }
-      if (!wait(p_full + 1, j & 1) || !wait_v(j)) break;
+      tc_fence_after();
       if (elect_one()) {
-        issue_pv(1, j);
-        umma_commit(v_free + (j & 1));
-        if (j + 1 == nB) umma_commit(o_full + 1);
+        issue_pv_wave(x, j, w);
+        if (w + 1 == kWaves) {
+          if (x == 1) umma_commit(v_free + (j & 1));
+          if (j + 1 == n_x) umma_commit(o_full + x);
+          if (j + 1 < n_x) {
+            issue_qk(x, j + 1);
+            if (x == 1) umma_commit(k_free + ((j + 1) & 1));
+          }
+        }
       }
       __syncwarp();
-      if (j + 1 < nB) {
-        if (!wait_k(j + 1)) break;
-        if (elect_one()) {
-          issue_qk(1, j + 1);
-          umma_commit(k_free + ((j + 1) & 1));
-        }
-        __syncwarp();
+      return true;
+    };
+    auto waves_of = [&](auto item, int j) -> bool {
+      bool good = step(item, std::integral_constant<int, 0>{}, j);
+      if constexpr (kWaves >= 2) good = good && step(item, std::integral_constant<int, 1>{}, j);
+      if constexpr (kWaves >= 4) {
+        good = good && step(item, std::integral_constant<int, 2>{}, j);
+        good = good && step(item, std::integral_constant<int, 3>{}, j);
       }
+      return good;
+    };
+    // The fixed order  PV_0(j) QK_0(j+1) | PV_1(j) QK_1(j+1)  keeps the two items half a period
+    // apart: the tensor pipe works on one while the other is in its softmax.  (Issuing whichever
+    // item is ready first was measured: the items fall into step, both softmax groups run at
+    // the same time and then both wait for the pipe, 285 against 249 us per layer.)
+    for (int j = 0; j < nB && ok; ++j) {
+      if (j < nA) ok = waves_of(std::integral_constant<int, 0>{}, j);
+      if (ok) ok = waves_of(std::integral_constant<int, 1>{}, j);
     }
   } else {
     // ===== softmax: warps 0..7 own item 0, warps 8..15 item 1.  Within an item warp w and warp
@@ -732,12 +801,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         return !failed;
       };
       for (int j = 0; j < n_mine; ++j) {
-        if (!wait_all(s_full + x, j & 1)) break;
-        softmax_tile<T>(tS, tO, lane_addr, row, half, p.qscale, j0 + j, j > 0, it.pos0, my_half, bar_id, st);
-        // this warp's part of P is in tensor memory
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(p_full + x);
+        const bool bad = !wait_or_abort(s_full + x, uint32_t(j & 1), abort_flag, p.wait_limit);
+        tc_fence_after();
+        if (!softmax_tile<T>(tS, tO, lane_addr, row, half, p.qscale, j0 + j, j > 0, it.pos0, my_half, bar_id, st, bad,
+                             flags + (warp & 15), uint32_t(j * kWaves), lane)) {
+          failed = true;
+          break;
+        }
       }
       if (!failed && wait_all(o_full + x, 0)) {
         if (pd.part < 0)
