@@ -81,7 +81,8 @@ struct PrefillParams {
   int32_t max_blocks_per_seq, num_q_heads, kv_mul;
   float qscale;  // softmax scale * log2(e)
   // Polls a bounded wait makes before it gives up (kWaitLimit), and, for the test of that path
-  // only, the CTA whose first K tile is announced to its barrier but never requested (-1: none).
+  // only, the CTA one of whose tiles is announced to its barrier but never requested (-1: none;
+  // the tile is chosen by the bits above the low 16, see the loader).
   uint32_t wait_limit;
   int32_t withhold_cta;
 };
@@ -626,7 +627,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (!ok) break;
         if (lane == 0) mbar_arrive_expect_tx(full, uint32_t(nblk) * (kBS * kD * 2));
         __syncwarp();
-        const bool withheld = int(blockIdx.x) == p.withhold_cta && j == 0 && kv == 0;  // test knob
+        // test knob: CTA (withhold_cta & 0xffff) never requests one tile it has announced:
+        // (withhold_cta >> 16) = 0: K of tile 0, 1: V of tile 0, 2: K of tile 1
+        const int what = p.withhold_cta >> 16;
+        const bool withheld = p.withhold_cta >= 0 && int(blockIdx.x) == (p.withhold_cta & 0xffff) &&
+                              j == (what == 2 ? 1 : 0) && kv == (what == 1 ? 1 : 0);
         if (lane < 2 * nblk && !withheld) {
           uint8_t* dst = (kv ? sV : sK) + stage * kOperandB + (lane & 1) * kChunkB + (lane >> 1) * (kBS * 128);
           tma_load_4d(dst, kv ? &map_v : &map_k, (lane & 1) * 64, 0, pd.kvh, id, full);
@@ -1049,8 +1054,10 @@ int64_t prefill_tc_area_bytes(int32_t total_q, int32_t num_q_heads) {
 }  // namespace kpx
 
 // Test knob (not in the public header): makes a bounded wait of the tensor-core kernel run out
-// without a faulting or endless kernel: CTA `withhold_cta` announces its first K tile to the
-// barrier but never requests it, and the waits give up after `wait_limit` polls (0: the default).
+// without a faulting or endless kernel: CTA (`withhold_cta` & 0xffff) announces one tile to its
+// barrier but never requests it (`withhold_cta` >> 16 = 0: K of its first key tile, 1: V of its
+// first key tile, 2: K of its second key tile), and the waits give up after `wait_limit` polls
+// (0: the default).
 extern "C" __attribute__((visibility("default"))) void kpx_internal_set_prefill_fault(uint32_t wait_limit, int withhold_cta) {
   kpx::g_prefill_wait_limit = wait_limit ? wait_limit : kpx::kWaitLimit;
   kpx::g_prefill_withhold_cta = withhold_cta;

@@ -66,10 +66,14 @@ def test_decode_wait_runs_out_and_the_workspace_recovers(native_libs, oracle, fo
     assert torch.equal(again.view(torch.uint8), good.view(torch.uint8)), "the launch after recovery differs"
 
 
-def test_prefill_wait_runs_out_and_the_next_call_is_right(native_libs, oracle):
-    """The tensor-core prefill kernel: one CTA never gets its first K tile; its roles give up in
-    step (the loader and the MMA warp on their barriers, the softmax threads by vote), tensor
-    memory is freed, the kernel returns, the status says so, and the same call made again is right."""
+@pytest.mark.parametrize("tile", [0, 1, 2], ids=["first_k_tile", "first_v_tile", "second_k_tile"])
+def test_prefill_wait_runs_out_and_the_next_call_is_right(native_libs, oracle, tile):
+    """The tensor-core prefill kernel: one CTA never gets one of its tiles (the first K tile: the
+    MMA warp gives up before its first scores; the first V tile or the second K tile: it gives
+    up inside its loop, on the progress words, with scores and weights of the first tile
+    already exchanged).  The roles give up in step (the loader on its barrier, the MMA warp on
+    the give-up word, the softmax threads by vote), tensor memory is freed, the kernel returns,
+    the status says so, and the same call made again is right."""
     import torch
     from orinmllm_b200 import capi
     H, HKV, D, n, start = 8, 2, 128, 300, 212
@@ -97,12 +101,15 @@ def test_prefill_wait_runs_out_and_the_next_call_is_right(native_libs, oracle):
     ref = oracle.mha_prefill(start, kvtest.storage_to_f32(q_st, "bf16"), H, length, HKV * D, H // HKV, D,
                              kc.reshape(-1), vc.reshape(-1), threads=oracle.max_threads())
     lib = capi.lib()
-    lib.kpx_internal_set_prefill_fault(3000, 0)
+    lib.kpx_internal_set_prefill_fault(3000, tile << 16)  # CTA 0, the tile chosen above
+    if tile:
+        lib.kpx_internal_set_prefill_split(0)  # whole pairs, so that CTA 0 has a second key tile
     try:
         broken = call()
         torch.cuda.synchronize()  # the kernel has returned
     finally:
         lib.kpx_internal_set_prefill_fault(0, -1)
+        lib.kpx_internal_set_prefill_split(-1)
     assert capi.workspace_status(ws) == capi.KPX_ERR_DEVICE_TIMEOUT
     # the withheld CTA's rows are missing: NaN where it owned them outright, wrong (its share of
     # the keys left out) where the call was cut along the keys and merged
