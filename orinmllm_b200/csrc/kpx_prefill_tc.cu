@@ -143,18 +143,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t* r) {
       : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t* r) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
-      "%29,%30,%31,%32};"
-      ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
-        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
-        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
 
 // Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte
 // offsets (all >> 4), version 1, 128-byte swizzle.
@@ -371,10 +359,11 @@ struct RowState {
 constexpr float kLazyMax = 8.f;
 
 // Softmax of key tile j of one item: S (tensor memory, 128 columns at tS) -> P over S, handed to
-// the MMA warp wave by wave (this warp's progress word counts the waves it has announced); O (which holds something when has_o) is
-// rescaled first where the row maximum moved.  Called by the 256 softmax threads of the item
-// (contains their barrier `bar_id`, which also carries the vote on `bad`: a thread whose wait for
-// S ran out).  Returns false, in all 256 threads alike, when any of them passed bad.
+// the MMA warp wave by wave (this warp's progress word counts the waves it has announced); O
+// (which holds something when has_o) is rescaled first where the row maximum moved.  Called by
+// the 256 softmax threads of the item (contains their barrier `bar_id`, which also carries the
+// vote on `bad`: a thread whose wait for S ran out).  Returns false, in all 256 threads alike,
+// when any of them passed bad.
 template <typename T>
 __device__ __forceinline__ bool softmax_tile(uint32_t tS, uint32_t tO, uint32_t lane_addr, int row, int half,
                                              float qscale, int j, bool has_o, int pos0, float* s_half,
@@ -637,8 +626,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           tma_load_4d(dst, kv ? &map_v : &map_k, (lane & 1) * 64, 0, pd.kvh, id, full);
         }
       }
-      // Tell the MMA warp what has landed (it reads plain words instead of polling these
-      // barriers itself: a poll of a barrier costs it about 200 clocks each time).
+      // Tell the MMA warp what has landed: it reads all it needs for a step with one load of
+      // the progress words instead of polling these barriers one after the other.
       if (ok) ok = wait_or_abort(k_full + stage, uint32_t(use & 1), abort_flag, p.wait_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (ok && lane == 0) flags[kKTilesWord] = uint32_t(j + 1);
@@ -717,12 +706,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     // This warp is one dependent instruction stream next to sixteen busy softmax warps, and what
     // it does between two batches of MMAs is time the tensor pipe stands still.  A per-step
-    // timeline showed a poll of a barrier in shared memory to cost it about 200 clocks, complete
-    // or not (1 650 of 4 650 clocks per key tile of the pair went into polls).  So it polls no
-    // barrier in the loop: the softmax warps and the loader publish their progress in plain
-    // words, and one load, lane i reading word i, shows everything a step needs: the item's
-    // eight softmax warps (lanes 0..7), the K and V tiles landed (lanes 8, 9), the give-up flag
-    // (lane 10).  The steps are unrolled with item and wave as constants.
+    // timeline showed every look at shared memory after a batch, a barrier poll or a plain load,
+    // to take it 200 - 350 clocks, complete or not, and a step needs up to four barriers.  So it
+    // polls no barrier in the loop: the softmax warps and the loader publish their progress in
+    // plain words, and ONE load, lane i reading word i, shows everything a step needs: the
+    // item's eight softmax warps (lanes 0..7), the K and V tiles landed (lanes 8, 9), the
+    // give-up flag (lane 10).  The steps are unrolled with item and wave as constants.
     const int word_other = lane < 8 ? 0 : lane < 11 ? lane + 8 : 19;  // lanes 8..10 read words 16..18, the rest a word that stays 0
     auto step = [&](auto item, auto wave, int j) -> bool {
       constexpr int x = decltype(item)::value, w = decltype(wave)::value;
