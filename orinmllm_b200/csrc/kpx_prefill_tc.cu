@@ -630,7 +630,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       // the progress words instead of polling these barriers one after the other.
       if (ok) ok = wait_or_abort(k_full + stage, uint32_t(use & 1), abort_flag, p.wait_limit);
       ok = __all_sync(0xffffffffu, ok);
-      if (ok && lane == 0) flags[kKTilesWord] = uint32_t(j + 1);
+      if (ok && lane == 0) {
+        __threadfence_block();
+        flags[kKTilesWord] = uint32_t(j + 1);
+      }
       if (ok) ok = wait_or_abort(v_full + stage, uint32_t(use & 1), abort_flag, p.wait_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (ok && ragged && j0 + j == tilesB - 1) {
