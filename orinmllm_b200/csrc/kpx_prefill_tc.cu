@@ -237,8 +237,8 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
   *abort_flag = 1;
   return false;
 }
-// Tiled TMA loads (no multicast): a box of the tensor map lands in shared memory, 128-byte
-// swizzled, and its bytes are counted on the mbarrier.
+// Tiled TMA loads, each into this CTA's own shared memory: a box of the tensor map lands there,
+// 128-byte swizzled, and its bytes are counted on the mbarrier.
 __device__ __forceinline__ void tma_load_3d(void* dst, const void* tmap, int c0, int c1, int c2, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
