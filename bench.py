@@ -106,9 +106,10 @@ class ClockSampler(threading.Thread):
 class DecodeWorkload:
     """Per-GPU state of the headline workload, resident in HBM."""
 
-    def __init__(self, rank, total_steps, device, chains=1, fused=True, world=1):
+    def __init__(self, rank, total_steps, device, chains=1, fused=True, world=1, use_plan=False):
         import torch
         self.chains, self.fused = chains, fused
+        self.use_plan = use_plan and not fused  # (the one-launch step takes no plan)
         self.per_layer = 1 if fused else 2
         from orinmllm_b200 import capi
         self.torch, self.capi, self.dev = torch, capi, device
@@ -164,6 +165,7 @@ class DecodeWorkload:
         for w in self.wss:
             capi.workspace_init(w, self.ws_bytes)
         self.ws = self.wss[0]
+        self.plan = torch.zeros(capi.decode_plan_bytes(), dtype=torch.uint8, device=device)
         self.scale = 1.0 / float(np.sqrt(HEAD))
         self.launches = 0
         # host side of the end-to-end path
@@ -190,7 +192,7 @@ class DecodeWorkload:
         self.cur_slots = self.torch.empty(BATCH, dtype=self.torch.int64, device=self.dev)
         self.graph_resident = self.graph_e2e = None
 
-    def layer(self, t, l, events=None, stream=None, ws=None, flags=0):
+    def layer(self, t, l, events=None, stream=None, ws=None, flags=0, plan=None):
         """RoPE + append + attend of layer l.  t: step index into the precomputed positions and
         slots, or None for the current-step buffers (graph capture)."""
         capi = self.capi
@@ -214,10 +216,16 @@ class DecodeWorkload:
         if events is not None:
             events[0].record()
         # tokens cached before the step + 1 appended = attended length (len_bias = 1)
-        decode = capi.paged_decode_overlapped if flags & capi.KPX_DECODE_OVERLAPPED else capi.paged_decode
-        decode(self.p_out[l], self.p_q[l], self.p_kpool[l], self.p_vpool[l], self.layout,
-               self.p_table, self.max_blocks, pos, 1, BATCH, Q_HEADS, self.scale,
-               self.p_ws if ws is None else ws, self.ws_bytes, stream=stream)
+        if plan is not None:
+            # the step's plan (made once per step, see capture): the same launch, shorter prologue
+            capi.paged_decode_planned(self.p_out[l], self.p_q[l], self.p_kpool[l], self.p_vpool[l], self.layout,
+                                      self.p_table, self.max_blocks, pos, 1, BATCH, Q_HEADS, self.scale,
+                                      self.p_ws if ws is None else ws, self.ws_bytes, plan, flags, stream=stream)
+        else:
+            decode = capi.paged_decode_overlapped if flags & capi.KPX_DECODE_OVERLAPPED else capi.paged_decode
+            decode(self.p_out[l], self.p_q[l], self.p_kpool[l], self.p_vpool[l], self.layout,
+                   self.p_table, self.max_blocks, pos, 1, BATCH, Q_HEADS, self.scale,
+                   self.p_ws if ws is None else ws, self.ws_bytes, stream=stream)
         if events is not None:
             events[1].record()
         self.launches += 2
@@ -255,13 +263,22 @@ class DecodeWorkload:
         flags = self.capi.KPX_DECODE_OVERLAPPED if self.chains > 1 else 0
         count = self.launches
 
+        plan = self.plan.data_ptr() if self.use_plan else None
+
+        def make_plan():
+            # one small launch per step: lengths and table are the same for all 36 layers
+            if plan is not None:
+                self.capi.decode_plan(plan, self.plan.numel(), self.layout, self.p_table, self.max_blocks,
+                                      self.cur_pos.data_ptr(), 1, BATCH, Q_HEADS, stream=main.cuda_stream)
+
         def run_layer(l):
             c = l % len(side)
-            self.layer(None, l, stream=side[c].cuda_stream, ws=self.wss[c].data_ptr(), flags=flags)
+            self.layer(None, l, stream=side[c].cuda_stream, ws=self.wss[c].data_ptr(), flags=flags, plan=plan)
             return side[c]
 
         self.graph_resident = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph_resident, stream=main):
+            make_plan()
             for s_ in side:
                 if s_ is not main:
                     s_.wait_stream(main)
@@ -272,6 +289,7 @@ class DecodeWorkload:
                     main.wait_stream(s_)
         self.graph_e2e = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph_e2e, stream=main):
+            make_plan()
             for s_ in [h2d, d2h] + [x for x in side if x is not main]:
                 s_.wait_stream(main)
             for l in range(LAYERS):
@@ -289,12 +307,12 @@ class DecodeWorkload:
     def replay_resident(self, t):
         self._set_step(t)
         self.graph_resident.replay()
-        self.launches += self.per_layer * LAYERS
+        self.launches += self.per_layer * LAYERS + (1 if self.use_plan else 0)
 
     def replay_e2e(self, t):
         self._set_step(t)
         self.graph_e2e.replay()
-        self.launches += self.per_layer * LAYERS
+        self.launches += self.per_layer * LAYERS + (1 if self.use_plan else 0)
 
     def kv_bytes_step(self, t):
         return kv_bytes_per_layer(self.lens0 + t + 1) * LAYERS
@@ -568,7 +586,7 @@ def run_gpu(args):
     use_graph = not args.no_graph
     total_steps = 2 * (W + K) + K + 2
     wl = DecodeWorkload(rank, total_steps, device, chains=max(1, args.chains) if use_graph else 1,
-                        fused=args.fused, world=world)
+                        fused=args.fused, world=world, use_plan=use_graph and not args.no_plan)
     if args.variant:
         wl.capi.lib().kpx_internal_set_decode_variant(args.variant)
 
@@ -667,10 +685,12 @@ def run_gpu(args):
         got, cpu_kind = cpu_decode_sample(1, 3), "port"
     cpu_gbs, cpu_sec, cpu_bytes = got
     chains = wl.chains if use_graph else 1
-    kernels = wl.per_layer * LAYERS
-    launch = ("one CUDA graph replay per step: %d kernels, layer l on chain l %% %d (layers are independent: own pool, "
+    kernels = wl.per_layer * LAYERS + (1 if wl.use_plan else 0)
+    launch = ("one CUDA graph replay per step: %d kernels%s, layer l on chain l %% %d (layers are independent: own pool, "
               "own rows, own workspace per chain), so a layer's CTAs take the SMs the previous layer's CTAs leave; "
-              "end to end: plus 36 H2D and 36 D2H copies on side streams" % (kernels, chains)) if use_graph \
+              "end to end: plus 36 H2D and 36 D2H copies on side streams"
+              % (kernels, " (the first one plans the step's 36 decode launches: kpx_decode_plan)" if wl.use_plan else "",
+                 chains)) if use_graph \
         else "one launch per kernel, one stream"
     line = {
         "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": K,
@@ -741,6 +761,8 @@ def main():
                     help="parallel chains the graph's independent layers are captured on")
     ap.add_argument("--fused", action="store_true",
                     help="one launch per layer (kpx_rope_append_decode) instead of kpx_rope_append + kpx_paged_decode")
+    ap.add_argument("--no-plan", action="store_true",
+                    help="decode launches work out their starting points themselves (no kpx_decode_plan per step)")
     ap.add_argument("--variant", type=int, default=0, help="decode tuning variant (experiments)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the prefill / append / prefix-reuse measurements after the headline")

@@ -162,6 +162,32 @@ KPX_API int kpx_paged_decode_overlapped(void* out, const void* q, const void* k_
                                         int32_t len_bias, int32_t batch, int32_t num_q_heads, float scale,
                                         void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Plan of a decode step.  All launches of one step (one per layer) see the same lengths and the
+ * same block table, so what each of them works out in its prologue (the block prefix over the
+ * sequences, every warp's starting point on the line of blocks, the id of its first block) is
+ * the same for all of them.  kpx_decode_plan works it out once into `plan` (device memory, 16-byte
+ * aligned, kpx_decode_plan_bytes() bytes); kpx_paged_decode_planned is kpx_paged_decode (flags 0)
+ * or kpx_paged_decode_overlapped (flags KPX_DECODE_OVERLAPPED) with that plan: a CTA then starts
+ * streaming after one load instead of three dependent ones.  Results are bit-identical with and
+ * without a plan.  The plan must have been made, earlier on the same stream or otherwise ordered
+ * before the launch, from the SAME block_table, seq_lens contents, len_bias, batch, head counts
+ * and cache dtype: make it again whenever a length or a table entry changes (every step).  A
+ * plan the launch cannot use (another batch or head layout, a batch of more than 512 sequences,
+ * a launch small enough for the short-range form, plan == NULL) is ignored and the launch works
+ * everything out itself; a plan that is out of date in its CONTENTS is the caller's error and is
+ * not detected.  A length in the plan that the table rows cannot hold raises the status word of
+ * the launch.  Capturable like kpx_paged_decode.  No reference counterpart (the reference
+ * passes one position per launch). */
+KPX_API int64_t kpx_decode_plan_bytes(void);
+KPX_API int kpx_decode_plan(void* plan, int64_t plan_bytes, const kpx_kv_layout* layout,
+                            const int32_t* block_table, int32_t max_blocks_per_seq, const int32_t* seq_lens,
+                            int32_t len_bias, int32_t batch, int32_t num_q_heads, void* stream);
+KPX_API int kpx_paged_decode_planned(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                     const kpx_kv_layout* layout, const int32_t* block_table,
+                                     int32_t max_blocks_per_seq, const int32_t* seq_lens, int32_t len_bias,
+                                     int32_t batch, int32_t num_q_heads, float scale, void* workspace,
+                                     int64_t workspace_bytes, const void* plan, int32_t flags, void* stream);
+
 /* One whole decode step of a layer in one launch: RoPE of the new token's Q and K rows,
  * append of its K / V rows to the pool, and the attention of kpx_paged_decode over the cached
  * tokens plus the new one.  positions[b] (device int32) is both the number of tokens sequence

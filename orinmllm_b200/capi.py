@@ -59,6 +59,10 @@ SIGNATURES = {
                                    _P, _I64, _P]),
     "kpx_paged_decode_overlapped": (C.c_int, [_P, _P, _P, _P, _LP, _P, _I32, _P, _I32, _I32, _I32, _F32,
                                               _P, _I64, _P]),
+    "kpx_decode_plan_bytes": (_I64, []),
+    "kpx_decode_plan": (C.c_int, [_P, _I64, _LP, _P, _I32, _P, _I32, _I32, _I32, _P]),
+    "kpx_paged_decode_planned": (C.c_int, [_P, _P, _P, _P, _LP, _P, _I32, _P, _I32, _I32, _I32, _F32,
+                                           _P, _I64, _P, _I32, _P]),
     "kpx_rope_append_decode": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _LP, _P, _I32, _P, _I32, _I32, _F32,
                                          _P, _I64, _I32, _P]),
     "kpx_paged_decode_static": (C.c_int, [_P, _P, _P, _P, _LP, _P, _I32, _P, _I32, _I32, _I32, _F32, _P]),
@@ -221,6 +225,27 @@ def paged_decode_overlapped(out, q, k_pool, v_pool, layout, block_table, max_blo
                                             ptr(block_table), max_blocks_per_seq, ptr(seq_lens), len_bias,
                                             batch, num_q_heads, scale, ptr(workspace), workspace_bytes,
                                             _stream(stream)), "kpx_paged_decode_overlapped")
+
+
+def decode_plan_bytes() -> int:
+    return lib().kpx_decode_plan_bytes()
+
+
+def decode_plan(plan, plan_bytes, layout, block_table, max_blocks_per_seq, seq_lens, len_bias, batch,
+                num_q_heads, stream=None) -> None:
+    """Works out once what every decode launch of a step would work out in its prologue."""
+    check(lib().kpx_decode_plan(ptr(plan), plan_bytes, C.byref(layout), ptr(block_table), max_blocks_per_seq,
+                                ptr(seq_lens), len_bias, batch, num_q_heads, _stream(stream)), "kpx_decode_plan")
+
+
+def paged_decode_planned(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq, seq_lens,
+                         len_bias, batch, num_q_heads, scale, workspace, workspace_bytes, plan, flags=0,
+                         stream=None) -> None:
+    """kpx_paged_decode / _overlapped (by flags) with the step's plan."""
+    check(lib().kpx_paged_decode_planned(ptr(out), ptr(q), ptr(k_pool), ptr(v_pool), C.byref(layout),
+                                         ptr(block_table), max_blocks_per_seq, ptr(seq_lens), len_bias,
+                                         batch, num_q_heads, scale, ptr(workspace), workspace_bytes,
+                                         ptr(plan), flags, _stream(stream)), "kpx_paged_decode_planned")
 
 
 def paged_decode_static(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq, seq_lens,

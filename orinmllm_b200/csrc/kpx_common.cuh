@@ -60,7 +60,7 @@ int decode_rows(void* out, const void* q, const void* k_pool, const void* v_pool
                 const kpx_kv_layout* layout, const int32_t* block_table, int32_t max_blocks_per_seq,
                 const int32_t* row_index, const int32_t* seq_lens, int32_t len_bias, int32_t batch,
                 int32_t num_q_heads, float scale, void* workspace, int64_t workspace_bytes,
-                void* stream, const FusedStep* fused = nullptr, int flags = 0);
+                void* stream, const FusedStep* fused = nullptr, int flags = 0, const void* plan = nullptr);
 
 // ---- device-side helpers -------------------------------------------------------------
 #ifdef __CUDACC__

@@ -77,6 +77,129 @@ extern "C" int kpx_paged_decode_overlapped(void* out, const void* q, const void*
                           stream, nullptr, KPX_DECODE_OVERLAPPED);
 }
 
+// ---------------------------------------------------------------------------------------
+// Plan of a decode step (layout: kpx_decode_impl.cuh).
+namespace kpx {
+namespace {
+constexpr int kPlanThreads = 128;
+// One thread per warp of the decode launch: where its range of the line of blocks starts.
+__global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeParams p, int32_t* plan, int workers) {
+  __shared__ int prefix[kMaxBatch + 1];
+  __shared__ int bad;
+  const int tid = threadIdx.x;
+  if (tid == 0) bad = 0;
+  for (int b = tid; b < p.batch; b += kPlanThreads) {
+    prefix[b + 1] = blocks_of(seq_len_of(p, b));
+    if (p.block_table && p.seq_lens && p.seq_lens[b] + p.len_bias > p.max_cached_tokens) bad = 1;
+  }
+  if (tid == 0) prefix[0] = 0;
+  __syncthreads();
+  if (tid < 32) {  // inclusive scan in chunks of 32
+    int carry = 0;
+    for (int base = 0; base < p.batch; base += 32) {
+      const int i = base + tid;
+      int v = i < p.batch ? prefix[i + 1] : 0;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, v, d);
+        if (tid >= d) v += n;
+      }
+      if (i < p.batch) prefix[i + 1] = v + carry;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int b = tid; b <= p.batch; b += kPlanThreads) plan[kPlanPrefixAt + b] = prefix[b];
+    if (tid == 0) {
+      plan[1] = p.batch;
+      plan[2] = workers;
+      plan[3] = p.num_kv_heads * p.head_groups;
+      plan[4] = bad ? KPX_ERR_INVALID_ARGUMENT : 0;
+      __threadfence();
+      plan[0] = kPlanMark;
+    }
+  }
+  const int w = blockIdx.x * kPlanThreads + tid;
+  if (w >= workers) return;
+  // the cut of the line and the search are the decode kernel's own (Split, Cursor::locate)
+  const int64_t total = int64_t(prefix[p.batch]) * p.num_kv_heads * p.head_groups;
+  Split split;
+  split.quot = total / workers;
+  split.rem = total - split.quot * workers;
+  const int64_t u0 = split.start(w), u1 = split.start(w + 1);
+  int4 e = make_int4(0xffff << 16, 0, 0, 0);
+  if (u0 < u1) {
+    Cursor cur;
+    cur.locate(p, prefix, u0);
+    e.x = (cur.b << 16) | cur.sub;
+    e.y = cur.blk;
+    e.z = cur.len;
+    e.w = cur.row ? cur.row[cur.blk] : cur.blk;
+  }
+  reinterpret_cast<int4*>(plan + kPlanEntriesAt)[w] = e;
+}
+}  // namespace
+}  // namespace kpx
+
+extern "C" int64_t kpx_decode_plan_bytes(void) {
+  return int64_t(kPlanEntriesAt + kMaxSms * kMaxWarpsPerCta * kPlanEntryWords) * 4;
+}
+
+extern "C" int kpx_decode_plan(void* plan, int64_t plan_bytes, const kpx_kv_layout* layout,
+                               const int32_t* block_table, int32_t max_blocks_per_seq, const int32_t* seq_lens,
+                               int32_t len_bias, int32_t batch, int32_t num_q_heads, void* stream) {
+  if (!layout_ok(layout) || !plan || (reinterpret_cast<uintptr_t>(plan) & 15) || batch < 0 || num_q_heads <= 0)
+    return KPX_ERR_INVALID_ARGUMENT;
+  if (plan_bytes < kpx_decode_plan_bytes()) return KPX_ERR_WORKSPACE_TOO_SMALL;
+  if (layout->head_size != kD || layout->block_size != kBS) return KPX_ERR_UNIMPLEMENTED;
+  if (num_q_heads % layout->num_kv_heads) return KPX_ERR_INVALID_ARGUMENT;
+  if (block_table && max_blocks_per_seq <= 0) return KPX_ERR_INVALID_ARGUMENT;
+  if (!seq_lens && len_bias < 0) return KPX_ERR_INVALID_ARGUMENT;
+  if (!device_info().ok) return KPX_ERR_CUDA;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (batch == 0 || batch > kMaxBatch) {
+    // nothing to plan, or a batch that decode serves in slices: a plan without its mark is ignored
+    return cuda_status(cudaMemsetAsync(plan, 0, 32, s));
+  }
+  DecodeParams p{};
+  p.block_table = block_table;
+  p.seq_lens = seq_lens;
+  p.row_index = nullptr;
+  p.max_blocks_per_seq = max_blocks_per_seq;
+  {
+    const int64_t row_tokens = int64_t(max_blocks_per_seq) * kBS;
+    p.max_cached_tokens = block_table ? int32_t(row_tokens > INT32_MAX ? INT32_MAX : row_tokens) : 0;
+  }
+  p.len_bias = len_bias;
+  p.batch = batch;
+  p.num_q_heads = num_q_heads;
+  p.num_kv_heads = layout->num_kv_heads;
+  p.kv_mul = num_q_heads / layout->num_kv_heads;
+  const int qh = heads_per_warp(p.kv_mul);
+  p.head_groups = (p.kv_mul + qh - 1) / qh;
+  // the warps of the launch forms that take a plan: 12 per SM for 16-bit caches (one CTA of 12
+  // or three of 4), 6 for fp32
+  int sms = device_info().sm_count;
+  if (sms > kMaxSms) sms = kMaxSms;
+  const int workers = sms * (layout->dtype == KPX_F32 ? 6 : 12);
+  decode_plan_kernel<<<(workers + kPlanThreads - 1) / kPlanThreads, kPlanThreads, 0, s>>>(
+      p, static_cast<int32_t*>(plan), workers);
+  return cuda_status(cudaGetLastError());
+}
+
+extern "C" int kpx_paged_decode_planned(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                        const kpx_kv_layout* layout, const int32_t* block_table,
+                                        int32_t max_blocks_per_seq, const int32_t* seq_lens, int32_t len_bias,
+                                        int32_t batch, int32_t num_q_heads, float scale, void* workspace,
+                                        int64_t workspace_bytes, const void* plan, int32_t flags, void* stream) {
+  if (flags & ~KPX_DECODE_OVERLAPPED) return KPX_ERR_INVALID_ARGUMENT;
+  if (plan && (reinterpret_cast<uintptr_t>(plan) & 15)) return KPX_ERR_INVALID_ARGUMENT;
+  return kpx::decode_rows(out, q, k_pool, v_pool, layout, block_table, max_blocks_per_seq, nullptr,
+                          seq_lens, len_bias, batch, num_q_heads, scale, workspace, workspace_bytes,
+                          stream, nullptr, flags, plan);
+}
+
 extern "C" int kpx_rope_append_decode(void* out, const void* q, const void* k_new, const void* v_new,
                                       const float* sin_cache, const float* cos_cache, void* k_pool,
                                       void* v_pool, const kpx_kv_layout* layout,
@@ -100,7 +223,7 @@ int kpx::decode_rows(void* out, const void* q, const void* k_pool, const void* v
                      int32_t max_blocks_per_seq, const int32_t* row_index, const int32_t* seq_lens,
                      int32_t len_bias, int32_t batch, int32_t num_q_heads, float scale,
                      void* workspace, int64_t workspace_bytes, void* stream, const FusedStep* fused,
-                     int flags) {
+                     int flags, const void* plan) {
   if (!layout_ok(layout) || !out || !q || !k_pool || !v_pool || batch < 0 || num_q_heads <= 0)
     return KPX_ERR_INVALID_ARGUMENT;
   if (layout->head_size != kD || layout->block_size != kBS) return KPX_ERR_UNIMPLEMENTED;
@@ -156,6 +279,8 @@ int kpx::decode_rows(void* out, const void* q, const void* k_pool, const void* v
   p.wait_limit = g_wait_limit;
   p.withhold_worker = g_withhold_worker;
   p.qscale = scale * kLog2e;
+  // a plan covers one launch of the whole batch as it is (no slices, no row indirection)
+  p.plan = (plan && batch <= kMaxBatch && !row_index && !fused) ? static_cast<const int32_t*>(plan) : nullptr;
   // the block prefix of one launch lives in shared memory: long batches go in slices
   for (int32_t b0 = 0; b0 < batch; b0 += kMaxBatch) {
     int32_t nb = batch - b0 < kMaxBatch ? batch - b0 : kMaxBatch;

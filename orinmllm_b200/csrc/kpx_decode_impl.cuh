@@ -77,7 +77,21 @@ struct DecodeParams {
   uint32_t wait_limit;
   int32_t withhold_worker;
   float qscale;  // softmax scale * log2(e)
+  // A plan of this step (nullptr: none), see the layout below: what every launch of the step
+  // would otherwise work out again in its prologue.
+  const int32_t* plan;
 };
+
+// Plan of one decode step.  The launches of a step (one per layer) all see the same lengths and
+// the same block table, so the block prefix over the sequences, every warp's starting point on
+// the line of blocks and the id of its first block are the same for all of them; with a plan a
+// CTA gets them with one load instead of three dependent ones (lengths, prefix and search, first
+// block id).  int32 words: [0] mark, [1] batch, [2] warps the line is cut for, [3] items per
+// sequence (kv heads x head groups), [4] an error to hand on (KPX_ERR_*), [8..8+kMaxBatch] the
+// block prefix, then one entry of four words per warp: (sequence << 16 | item, block, tokens of
+// the sequence, id of that block); sequence 0xffff = the warp has no blocks.
+constexpr int32_t kPlanMark = 0x4b50504c;
+constexpr int kPlanPrefixAt = 8, kPlanEntriesAt = kPlanPrefixAt + kMaxBatch + 8, kPlanEntryWords = 4;
 
 template <typename T, int QH, int NW, int NS, int LPT>
 struct Cfg {
@@ -108,6 +122,34 @@ __device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
   return len < 0 ? 0 : len;
 }
 __device__ __forceinline__ int blocks_of(int len) { return (len + kBS - 1) / kBS; }
+
+// prefix[b] = blocks of sequences 0..b-1 (prefix[0] = 0), worked out by the whole CTA; `report`:
+// this CTA raises the status word for a length the table rows cannot hold.
+__device__ __forceinline__ void block_prefix(const DecodeParams& p, int* prefix, int tid, int nthreads, int warp,
+                                             int lane, bool report) {
+  for (int b = tid; b < p.batch; b += nthreads) {
+    prefix[b + 1] = blocks_of(seq_len_of(p, b));
+    if (p.block_table && p.seq_lens && report && p.seq_lens[b] + p.len_bias > p.max_cached_tokens)
+      atomicMax(p.status, KPX_ERR_INVALID_ARGUMENT);
+  }
+  if (tid == 0) prefix[0] = 0;
+  __syncthreads();
+  if (warp == 0) {  // inclusive scan in chunks of 32
+    int carry = 0;
+    for (int base = 0; base < p.batch; base += 32) {
+      int i = base + lane;
+      int v = i < p.batch ? prefix[i + 1] : 0;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d) v += n;
+      }
+      if (i < p.batch) prefix[i + 1] = v + carry;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  __syncthreads();
+}
 
 // Position on the line of blocks: sequence b, sub-item (= kv_head*head_groups +
 // head_group), block blk of the sequence.  kvh and the block-table row of b are
@@ -261,28 +303,25 @@ paged_decode_kernel(const DecodeParams p) {
     for (int s = 0; s < 2 * NS; ++s) mbar_init(bars + s, 1);
     mbar_fence_init();
   }
-  for (int b = tid; b < p.batch; b += C::kThreads) {
-    prefix[b + 1] = blocks_of(seq_len_of(p, b));
-    if (p.block_table && p.seq_lens && blockIdx.x == 0 && p.seq_lens[b] + p.len_bias > p.max_cached_tokens)
-      atomicMax(p.status, KPX_ERR_INVALID_ARGUMENT);
-  }
-  if (tid == 0) prefix[0] = 0;
-  __syncthreads();
-  if (warp == 0) {  // inclusive scan in chunks of 32
-    int carry = 0;
-    for (int base = 0; base < p.batch; base += 32) {
-      int i = base + lane;
-      int v = i < p.batch ? prefix[i + 1] : 0;
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        int n = __shfl_up_sync(0xffffffffu, v, d);
-        if (lane >= d) v += n;
-      }
-      if (i < p.batch) prefix[i + 1] = v + carry;
-      carry += __shfl_sync(0xffffffffu, v, 31);
+  // With a plan of the step the prefix and this warp's starting point come from it: one round
+  // trip to global memory instead of lengths -> prefix -> search -> first block id.
+  bool planned = false;
+  int4 plan_entry = make_int4(0, 0, 0, 0);
+  if constexpr (!kSmall && !kFused) {
+    if (p.plan) {
+      const int32_t* h = p.plan;
+      planned = h[0] == kPlanMark && h[1] == p.batch && h[2] == int(gridDim.x) * C::kWarps &&
+                h[3] == p.num_kv_heads * p.head_groups;
     }
   }
-  __syncthreads();
+  if (planned) {
+    plan_entry = __ldg(reinterpret_cast<const int4*>(p.plan + kPlanEntriesAt) + (blockIdx.x * C::kWarps + warp));
+    for (int b = tid; b <= p.batch; b += C::kThreads) prefix[b] = __ldg(p.plan + kPlanPrefixAt + b);
+    if (blockIdx.x == 0 && tid == 0 && p.plan[4] != 0) atomicMax(p.status, p.plan[4]);
+    __syncthreads();
+  } else {
+    block_prefix(p, prefix, tid, C::kThreads, warp, lane, blockIdx.x == 0);
+  }
   // a sequence without tokens gets zeros (no warp ever visits it); CTAs share the rows.
   // In the fused step its only token is the new one: every head's output is that token's V
   // row, and its rotated K (position 0: unchanged) and V rows go to slot 0 of its first block.
@@ -358,7 +397,16 @@ paged_decode_kernel(const DecodeParams p) {
   // output pass trails the score pass by one block), reusing the source offset and
   // row count remembered from the K request.
   Cursor cur;  // consumer side: first block of the current segment
-  cur.locate(p, prefix, u0);
+  if (planned) {
+    cur.b = plan_entry.x >> 16;
+    cur.sub = plan_entry.x & 0xffff;
+    cur.blk = plan_entry.y;
+    cur.len = plan_entry.z;
+    cur.nblk = prefix[cur.b + 1] - prefix[cur.b];
+    cur.refresh(p);
+  } else {
+    cur.locate(p, prefix, u0);
+  }
   // The first item's query rows are requested here, before the first block id and the first
   // tiles, so that their latency (DRAM if nothing brought them to L2) runs under those.
   uint4 q_first[kFused ? 1 : QH][kFused ? 1 : NCH];
@@ -416,7 +464,15 @@ paged_decode_kernel(const DecodeParams p) {
     copy_tile(p.v_pool, last_off, last_rows, NS + slot);
     ++v_issued;
   };
-  pc_id = load_id();
+  if (planned) {
+    pc_id = plan_entry.w;
+    if (pc_id < 0 || (p.num_blocks > 0 && pc_id >= p.num_blocks)) {
+      if (lane == 0) atomicMax(p.status, KPX_ERR_INVALID_ARGUMENT);
+      pc_id = 0;
+    }
+  } else {
+    pc_id = load_id();
+  }
 #pragma unroll
   for (int k = 0; k < NS; ++k) {
     if (k < n) {
