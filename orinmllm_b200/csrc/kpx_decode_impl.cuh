@@ -309,19 +309,20 @@ paged_decode_kernel(const DecodeParams p) {
   int4 plan_entry = make_int4(0, 0, 0, 0);
   if constexpr (!kSmall && !kFused) {
     if (p.plan) {
-      const int32_t* h = p.plan;
-      planned = h[0] == kPlanMark && h[1] == p.batch && h[2] == int(gridDim.x) * C::kWarps &&
-                h[3] == p.num_kv_heads * p.head_groups;
+      // header, this warp's entry and the prefix are requested together (a plan buffer always
+      // holds kMaxSms x 16 entries and kMaxBatch + 1 prefix words, whatever was planned); what
+      // the header says decides afterwards whether they are used
+      const int4 h = __ldg(reinterpret_cast<const int4*>(p.plan));
+      const int32_t plan_error = __ldg(p.plan + 4);
+      plan_entry = __ldg(reinterpret_cast<const int4*>(p.plan + kPlanEntriesAt) + (blockIdx.x * C::kWarps + warp));
+      for (int b = tid; b <= p.batch; b += C::kThreads) prefix[b] = __ldg(p.plan + kPlanPrefixAt + b);
+      planned = h.x == kPlanMark && h.y == p.batch && h.z == int(gridDim.x) * C::kWarps &&
+                h.w == p.num_kv_heads * p.head_groups;
+      if (planned && blockIdx.x == 0 && tid == 0 && plan_error != 0) atomicMax(p.status, plan_error);
+      __syncthreads();
     }
   }
-  if (planned) {
-    plan_entry = __ldg(reinterpret_cast<const int4*>(p.plan + kPlanEntriesAt) + (blockIdx.x * C::kWarps + warp));
-    for (int b = tid; b <= p.batch; b += C::kThreads) prefix[b] = __ldg(p.plan + kPlanPrefixAt + b);
-    if (blockIdx.x == 0 && tid == 0 && p.plan[4] != 0) atomicMax(p.status, p.plan[4]);
-    __syncthreads();
-  } else {
-    block_prefix(p, prefix, tid, C::kThreads, warp, lane, blockIdx.x == 0);
-  }
+  if (!planned) block_prefix(p, prefix, tid, C::kThreads, warp, lane, blockIdx.x == 0);
   // a sequence without tokens gets zeros (no warp ever visits it); CTAs share the rows.
   // In the fused step its only token is the new one: every head's output is that token's V
   // row, and its rotated K (position 0: unchanged) and V rows go to slot 0 of its first block.
