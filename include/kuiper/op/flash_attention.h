@@ -86,6 +86,9 @@ class FlashAttentionDecodeLayer : public Layer {
     paged_.batch = batch;
     paged_.num_blocks = num_blocks;
   }
+  // the plan of the decode step (MultiHeadAttention::plan_decode_step); an empty tensor: none
+  void set_plan(const tensor::Tensor& plan) { paged_.plan = plan; }
+  const PagedArgs& paged_args() const { return paged_; }
 
  private:
   int32_t head_num_ = 0, kv_head_num_ = 0, head_size_ = 0, kv_mul_ = 0, seq_len_ = 0, kv_dim_ = 0;

@@ -18,6 +18,10 @@ struct PagedArgs {
   tensor::Tensor seq_lens;     // int32 [batch] on the device: tokens cached, the new one included
   int32_t batch = 0;
   int64_t num_blocks = 0;      // blocks in the pool (0: ids are not range-checked)
+  // Optional: the plan of this decode step (kpx_decode_plan_bytes() bytes on the device, made
+  // by MultiHeadAttention::plan_decode_step after the step's lengths were written and before the
+  // first layer's attention).  Every layer of the step may carry the same plan.
+  tensor::Tensor plan;
 };
 
 class MultiHeadAttention : public op::Layer {
@@ -41,6 +45,9 @@ class MultiHeadAttention : public op::Layer {
     paged_.batch = batch;
     paged_.num_blocks = num_blocks;
   }
+  // the plan of the decode step (MultiHeadAttention::plan_decode_step); an empty tensor: none
+  void set_plan(const tensor::Tensor& plan) { paged_.plan = plan; }
+  const PagedArgs& paged_args() const { return paged_; }
 
   base::Status check() const override {
     const base::DataType dt = get_input(0).data_type();
@@ -78,12 +85,42 @@ class MultiHeadAttention : public op::Layer {
     int rc = kpx_layout_paged(&lay, kernel::detail::kpx_dtype(k_pool), kv_heads, head_size, 16);
     if (rc != KPX_OK) return base::Status(rc, kpx_status_string(rc));
     lay.num_blocks = pa.num_blocks;
+    const float scale = 1.f / std::sqrt(static_cast<float>(head_size));
+    if (!pa.plan.is_empty() && config) {
+      // with a plan: the workspace form (the plan shortens every launch's prologue)
+      const int64_t need = kpx_decode_workspace_bytes(pa.batch, head_num, kv_heads, head_size);
+      if (need >= 0 && config->ensure_kv_workspace(static_cast<size_t>(need))) {
+        rc = kpx_paged_decode_planned(const_cast<uint8_t*>(out.ptr<uint8_t>()), query.ptr<uint8_t>(),
+                                      k_pool.ptr<uint8_t>(), v_pool.ptr<uint8_t>(), &lay,
+                                      pa.block_table.ptr<int32_t>(),
+                                      pa.block_table.get_dim(pa.block_table.dims_size() - 1),
+                                      pa.seq_lens.ptr<int32_t>(), 0, pa.batch, head_num, scale, config->kv_workspace,
+                                      static_cast<int64_t>(config->kv_workspace_bytes), pa.plan.ptr<uint8_t>(), 0,
+                                      config->stream);
+        return rc == KPX_OK ? base::error::Success() : base::Status(rc, kpx_status_string(rc));
+      }
+    }
     rc = kernel::detail::decode_any(const_cast<uint8_t*>(out.ptr<uint8_t>()), query.ptr<uint8_t>(),
                                     k_pool.ptr<uint8_t>(), v_pool.ptr<uint8_t>(), &lay,
                                     pa.block_table.ptr<int32_t>(),
                                     pa.block_table.get_dim(pa.block_table.dims_size() - 1),
-                                    pa.seq_lens.ptr<int32_t>(), 0, pa.batch, head_num,
-                                    1.f / std::sqrt(static_cast<float>(head_size)), config);
+                                    pa.seq_lens.ptr<int32_t>(), 0, pa.batch, head_num, scale, config);
+    return rc == KPX_OK ? base::error::Success() : base::Status(rc, kpx_status_string(rc));
+  }
+
+  // Once per decode step, after the step's lengths are in pa.seq_lens: fills pa.plan, which the
+  // attention layers of all the model's layers then carry (set_paged with the same PagedArgs).
+  // `k_pool`: any layer's K pool (for the cache's element type).
+  static base::Status plan_decode_step(const PagedArgs& pa, const tensor::Tensor& k_pool, int32_t head_num,
+                                       int32_t kv_heads, int32_t head_size, kernel::CudaConfig* config) {
+    if (pa.plan.is_empty()) return base::error::InvalidArgument("plan_decode_step: no plan buffer");
+    kpx_kv_layout lay;
+    int rc = kpx_layout_paged(&lay, kernel::detail::kpx_dtype(k_pool), kv_heads, head_size, 16);
+    if (rc != KPX_OK) return base::Status(rc, kpx_status_string(rc));
+    lay.num_blocks = pa.num_blocks;
+    rc = kpx_decode_plan(const_cast<uint8_t*>(pa.plan.ptr<uint8_t>()), static_cast<int64_t>(pa.plan.byte_size()), &lay,
+                         pa.block_table.ptr<int32_t>(), pa.block_table.get_dim(pa.block_table.dims_size() - 1),
+                         pa.seq_lens.ptr<int32_t>(), 0, pa.batch, head_num, config ? config->stream : nullptr);
     return rc == KPX_OK ? base::error::Success() : base::Status(rc, kpx_status_string(rc));
   }
 

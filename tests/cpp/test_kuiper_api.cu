@@ -298,6 +298,19 @@ static void test_paged_layers_fp16() {
   fa.set_input(0, dq); fa.set_input(1, dout); fa.set_input(2, kpool); fa.set_input(3, vpool);
   EXPECT(bool(fa.forward()));
   cudaStreamSynchronize(cfg->stream);
+  // the same step with a plan (made once per step, carried by every layer): the same bits
+  {
+    tensor::Tensor plan(DataType::kDataTypeInt8, int32_t(kpx_decode_plan_bytes()), true, cuda_alloc());
+    fa.set_plan(plan);
+    EXPECT(bool(op::MultiHeadAttention::plan_decode_step(fa.paged_args(), kpool, H, HKV, D, cfg.get())));
+    tensor::Tensor dout2(DataType::kDataTypeFp16, B, dim, true, cuda_alloc());
+    fa.set_input(1, dout2);
+    EXPECT(bool(fa.forward()));
+    cudaStreamSynchronize(cfg->stream);
+    std::vector<__half> a1 = to_host<__half>(dout), a2 = to_host<__half>(dout2);
+    EXPECT(std::memcmp(a1.data(), a2.data(), a1.size() * sizeof(__half)) == 0);
+    std::printf("  with the step's plan: identical output\n");
+  }
   std::vector<float> got = from_half(to_host<__half>(dout)), qf = from_half(q);
   for (int b = 0; b < B; ++b) {
     std::vector<float> score(size_t(H) * lens[b]), ref(dim);
