@@ -50,6 +50,7 @@ class ServingSim:
                             capi.decode_workspace_bytes(max_decode_batch, q_heads, kv_heads, self.D))
         self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device="cuda")
         capi.workspace_init(self.ws, self.ws_bytes)
+        self.plan = torch.zeros(capi.decode_plan_bytes(), dtype=torch.uint8, device="cuda")
         self.record = record
         self.record_ids = None if record_ids is None else set(int(r) for r in record_ids)  # None: every request
         self.outputs = {}       # request id -> {position: [L, dim] output rows (host, float32)} when record
@@ -105,6 +106,8 @@ class ServingSim:
         q_all, k_all, v_all = self._rows(ids)
         rows = len(d.request_ids)
         outs = []
+        # the step's plan: lengths and table are the same for every layer of the step
+        capi.decode_plan(self.plan, self.plan.numel(), self.layout, table, table.shape[1], lens, 0, rows, self.H)
         for l in range(self.L):
             q, k, v = q_all[l].contiguous(), k_all[l].contiguous(), v_all[l].contiguous()
             capi.rope_append(q, k, v, self.H, pos, self.sin, self.cos, self.kp[l], self.vp[l], self.layout, slots,
@@ -113,8 +116,8 @@ class ServingSim:
             if self.decode_events is not None:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-            capi.paged_decode(out, q, self.kp[l], self.vp[l], self.layout, table, table.shape[1], lens, 0, rows,
-                              self.H, self.scale, self.ws, self.ws_bytes)
+            capi.paged_decode_planned(out, q, self.kp[l], self.vp[l], self.layout, table, table.shape[1], lens, 0,
+                                      rows, self.H, self.scale, self.ws, self.ws_bytes, self.plan)
             if self.decode_events is not None:
                 e1.record()
                 self.decode_events.append((e0, e1, int(d.seq_lens.sum()) * self.HKV * self.D * self.kp.element_size() * 2))
